@@ -1,0 +1,235 @@
+/* libnfai_cuda.so -- C ABI of the B200 (sm_100a) Llama-3 forward path for NFAI.
+ *
+ * This library stands where the reference's NFAI.Vulkan + NFAI.Vulkan.Shaders projects stand: device context,
+ * weight upload, KV cache, the per-token transformer schedule and every compute kernel. The managed side
+ * (Parser, LlamaModelFactory, LlamaModel, GenericChatClient, ComputeCollection) keeps its shape and calls these
+ * entry points through P/Invoke. Every comment "replaces:" cites the reference code (path within the
+ * reference project : lines) whose job the entry point takes over.
+ *
+ * Conventions
+ *  - every function returns an int status (NFAI_OK == 0) unless stated otherwise;
+ *  - handles are opaque; a handle is used by one thread at a time (the reference drives its device from one
+ *    managed thread: NFAI.Models.Llama3/LlamaModel.cs:99-174); different contexts may live on different threads;
+ *  - host pointers are owned by the caller and are fully consumed before the call returns;
+ *  - the library owns all device memory behind nfai_ctx / nfai_model handles;
+ *  - nothing here exits, aborts or traps: failures come back as a status plus nfai_last_error().
+ *  - entry points named nfai_op_* take DEVICE pointers and run one kernel of the path on caller-owned buffers.
+ */
+#ifndef NFAI_CUDA_H
+#define NFAI_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct nfai_ctx nfai_ctx;
+typedef struct nfai_model nfai_model;
+
+enum {
+  NFAI_OK = 0,
+  NFAI_ERR_ARG = 1,          /* bad argument (null, out of range, wrong dtype, unknown tensor name) */
+  NFAI_ERR_STATE = 2,        /* call made in the wrong lifecycle state */
+  NFAI_ERR_OOM = 3,          /* device or pinned host allocation failed */
+  NFAI_ERR_CUDA = 4,         /* a CUDA runtime call or kernel failed */
+  NFAI_ERR_NCCL = 5,         /* an NCCL call failed or NCCL is not loadable */
+  NFAI_ERR_CONTEXT_FULL = 6, /* position would reach the KV-cache capacity */
+  NFAI_ERR_TIMEOUT = 7       /* a bounded device-side wait gave up */
+};
+
+enum { NFAI_F32 = 0, NFAI_F16 = 1 };
+
+/* Model geometry. Mirrors what the reference reads from GGUF metadata
+ * (NFAI.Models.Llama3/LlamaModel.cs:23-39) plus ModelOptions.KVCacheSize (NFAI.Models/ModelOptions.cs:3-8). */
+typedef struct nfai_hparams {
+  uint32_t H;        /* llama.embedding_length (= token_embd ne0) */
+  uint32_t L;        /* llama.block_count */
+  uint32_t qH;       /* llama.attention.head_count */
+  uint32_t kvH;      /* llama.attention.head_count_kv */
+  uint32_t d;        /* llama.attention.key_length (head dim) */
+  uint32_t ropeDim;  /* llama.rope.dimension_count */
+  uint32_t F;        /* FFN width (ffn_gate ne1) */
+  uint32_t V;        /* vocabulary (token_embd ne1) */
+  uint32_t ctx;      /* KV-cache capacity in positions (ModelOptions.KVCacheSize) */
+  float eps;         /* RMSNorm epsilon; also the softmax guard (NFAI.Vulkan.Shaders/TransformerBlock.cs:115-116) */
+  float rope_theta;  /* RoPE base; the reference hard-codes 500000 (TransformerBlock.cs:33) */
+  int32_t weight_dtype; /* NFAI_F32 or NFAI_F16: how matrices are kept in HBM */
+  int32_t kv_dtype;     /* NFAI_F32 (the reference's cache type) or NFAI_F16 */
+  int32_t tied;         /* 1: LM head = token_embd (LlamaModel.cs:64-67); 0: output.weight is uploaded */
+} nfai_hparams;
+
+/* ---- library ------------------------------------------------------------------------------------------- */
+
+/* Version string of the library (static storage). */
+const char* nfai_version(void);
+
+/* Text of the last failure on this context (static per context; empty string if none). ctx may be NULL, in
+ * which case the last failure of a call that had no context (e.g. nfai_ctx_create) is returned.
+ * replaces: generic Exception messages at NFAI.Vulkan/VulkanBufferManager.cs:61-87. */
+const char* nfai_last_error(const nfai_ctx* ctx);
+
+/* ---- device context ------------------------------------------------------------------------------------ */
+
+/* Open CUDA device `device_ordinal`, create the stream, the pinned staging ring and the timing events.
+ * replaces: LlamaModelFactory() ctor (NFAI.Models.Llama3/LlamaModelFactory.cs:15-22) and
+ *           VulkanHelper.CreateVulkanInstance/PickPhysicalDevice/CreateLogicalDevice
+ *           (NFAI.Vulkan/VulkanHelper.cs:11,136,153). */
+int nfai_ctx_create(int device_ordinal, nfai_ctx** out);
+
+/* Fill `out` (at least 128 bytes) with a fresh NCCL unique id; rank 0 makes it and the host shares it with the
+ * other ranks by any means. No counterpart in the reference (single device). */
+int nfai_tp_unique_id(void* out, size_t out_bytes);
+
+/* Like nfai_ctx_create, for rank `rank` of a `world`-way tensor-parallel group (world in {1,2,4,8}); joins the
+ * NCCL communicator named by `nccl_uid`. One context per GPU: either one process per GPU or one thread per GPU.
+ * No counterpart in the reference (single device). */
+int nfai_ctx_create_tp(int device_ordinal, int rank, int world, const void* nccl_uid, size_t uid_bytes,
+                       nfai_ctx** out);
+
+/* replaces: LlamaModelFactory.Dispose (LlamaModelFactory.cs:24-32). */
+int nfai_ctx_destroy(nfai_ctx* ctx);
+
+/* ---- model lifecycle: create -> tensors -> finalize -> prefill/decode -> destroy ----------------------- */
+
+/* replaces: LlamaModel ctor reading hyper-parameters (LlamaModel.cs:21-41). */
+int nfai_model_create(nfai_ctx* ctx, const nfai_hparams* hp, nfai_model** out);
+
+/* Start uploading the tensor `gguf_name` (e.g. "blk.3.attn_q.weight"). `shape` is in GGUF ne order (innermost
+ * first), as NFAI.GGUF/Parser.cs:252-258 reads it. `src_dtype` is the element type of the bytes that follow:
+ * NFAI_F32 (what ComputeCollection.GetDataRaw yields today, halves already widened:
+ * NFAI.Core/AbstractComputeCollection.cs:62-77) or NFAI_F16 (raw file bytes). Conversion to the model's
+ * weight_dtype happens on the device; F32 -> F16 is exact for values that were widened from halves.
+ * Under tensor parallelism the caller streams the WHOLE tensor; each rank keeps its shard.
+ * replaces: ShaderProperty.SetValue(ComputeCollection) -> VulkanBufferManager.UploadDataToDeviceLocal
+ *           (NFAI.Vulkan/VulkanBufferManager.cs:105-194) and the name lookups at
+ *           NFAI.Vulkan.Shaders/TransformerBlock.cs:41-99, LlamaModel.cs:43,58. */
+int nfai_model_tensor_begin(nfai_model* m, const char* gguf_name, int src_dtype, const uint64_t* shape, int ndim);
+
+/* Next `nbytes` of the tensor opened by nfai_model_tensor_begin, in file order; any chunking is accepted as
+ * long as nbytes is a multiple of the source element size. */
+int nfai_model_tensor_chunk(nfai_model* m, const void* bytes, size_t nbytes);
+
+/* Close the tensor; fails if fewer or more bytes arrived than the shape needs. */
+int nfai_model_tensor_end(nfai_model* m);
+
+/* All tensors are in: check completeness, build the RoPE table on the host in float32
+ * (TransformerBlock.cs:33-38), allocate the KV cache and activations, capture the decode graph.
+ * replaces: the buffer-aliasing graph wiring of TransformerBlock ctor (TransformerBlock.cs:49-124) and
+ *           ShaderWrapper.Compile on first use (NFAI.Vulkan.Shaders/ShaderWrapper.cs:55-206). */
+int nfai_model_finalize(nfai_model* m);
+
+/* replaces: LlamaModel.Dispose (LlamaModel.cs:70-74, which throws NotImplementedException). */
+int nfai_model_destroy(nfai_model* m);
+
+/* ---- the hot path --------------------------------------------------------------------------------------- */
+
+/* Ingest `n` prompt tokens at positions pos..pos+n-1. If `logits_last` is non-null it receives the V float32
+ * logits of the last token; if `argmax_last` is non-null it receives the lowest index of their maximum.
+ * The result equals feeding the tokens one by one through nfai_decode.
+ * replaces: the prompt loop of LlamaModel.RunAsync (LlamaModel.cs:103-126). */
+int nfai_prefill(nfai_model* m, const uint32_t* tokens, int n, float* logits_last, uint32_t* argmax_last);
+
+/* One token at the current position: embed -> L x block -> output norm -> LM head. `logits` (V floats) and
+ * `argmax` are optional host outputs. Advances the position by one.
+ * replaces: one iteration of the decode loop (LlamaModel.cs:134-173): TokenEmbedShader.Compute,
+ *           TransformerBlock.Compute (NFAI.Vulkan.Shaders/TransformerBlock.cs:127-184), output RMSNorm, LM-head
+ *           MatrixMultiplyShader, GetOutputs; and SamplingUtils.ArgMax (NFAI.Models.Llama3/SamplingUtils.cs:55-56). */
+int nfai_decode(nfai_model* m, uint32_t token, float* logits, uint32_t* argmax);
+
+/* Greedy generation that never leaves the device: feed `first_token`, then feed each arg-max back, `n_steps`
+ * times. `out_tokens` (n_steps entries, host, optional) receives the arg-max of every step; `elapsed_ms`
+ * (optional) the device time of the n_steps steps measured with CUDA events on the library's stream.
+ * replaces: the decode loop of LlamaModel.RunAsync with SamplingUtils.ArgMax in place of TopP. */
+int nfai_decode_greedy(nfai_model* m, uint32_t first_token, int n_steps, uint32_t* out_tokens, float* elapsed_ms);
+
+/* Current position (number of tokens in the KV cache).
+ * replaces: TransformerBlock.currentToken (TransformerBlock.cs:25,183) and
+ *           MatrixMultiplyShader.currentCacheSize (NFAI.Vulkan.Shaders/MatrixMultiplyShader.cs:28). */
+int nfai_position(const nfai_model* m, uint32_t* pos);
+
+/* Position back to 0 (the KV cache content is left in place and overwritten as positions are reused).
+ * replaces: MatrixMultiplyShader.ResetCache (MatrixMultiplyShader.cs:153-159). */
+int nfai_reset(nfai_model* m);
+
+/* ---- taps for parity tests ------------------------------------------------------------------------------ */
+
+/* K and V rows (kvH*d floats each, widened to float32) of `layer` at `pos`. Under tensor parallelism the rank's
+ * own KV heads come back in the first kvH*d/world floats.
+ * replaces: MatrixMultiplyShader.GetCurrentCache (MatrixMultiplyShader.cs:313-316). */
+int nfai_read_kv(nfai_model* m, uint32_t layer, uint32_t pos, float* k, float* v);
+
+/* Overwrite K and V rows of `layer` at `pos` from float32 host data (used to seed long-context tests). */
+int nfai_write_kv(nfai_model* m, uint32_t layer, uint32_t pos, const float* k, const float* v);
+
+/* Set the position without touching the cache (pairs with nfai_write_kv). */
+int nfai_set_position(nfai_model* m, uint32_t pos);
+
+/* Residual stream (H floats) after block `layer` for the token processed last.
+ * replaces: TransformerBlock.GetOutputProperty().GetValue() (TransformerBlock.cs:210-213). */
+int nfai_read_hidden(nfai_model* m, uint32_t layer, float* out);
+
+/* ---- measurement ---------------------------------------------------------------------------------------- */
+
+/* Time `iters` back-to-back launches of one kernel of the decode step on the library's stream with CUDA
+ * events; launch i uses layer (i mod L)'s weights so that consecutive launches read different HBM.
+ * which: 0 = FFN gate/up GEMV (+RMSNorm, +SiLU*up), 1 = FFN down GEMV (+residual), 2 = QKV GEMV (+RMSNorm,+RoPE),
+ *        3 = O-projection GEMV (+residual), 4 = LM-head GEMV (+RMSNorm, +arg-max partials), 5 = attention.
+ * avg_ms receives the mean duration of one launch; bytes_per_launch the algorithmic bytes it must move. */
+int nfai_profile_kernel(nfai_model* m, int which, int iters, float* avg_ms, uint64_t* bytes_per_launch);
+
+/* Number of kernel launches inside one decode step (the captured graph's kernel nodes). */
+int nfai_step_launches(const nfai_model* m, int* out);
+
+/* ---- single kernels on caller-owned DEVICE buffers (kernel-level parity tests, embedding in other hosts) - */
+
+/* x_out[i] = E[H*token + i] widened to float32.
+ * replaces: TokenEmbedShader (NFAI.Vulkan.Shaders/TokenEmbedShader.cs:139-158). */
+int nfai_op_embed(nfai_ctx* ctx, const void* E, int dtype, uint32_t H, uint32_t V, uint32_t token, float* x_out);
+
+/* y = W * f(x) (+ resid): W[N][K] row-major of `dtype`; f = RMSNorm with `gain` and `eps` when gain != NULL,
+ * identity otherwise; resid (N floats) optional. All pointers are device pointers.
+ * replaces: RMSNormShader (NFAI.Vulkan.Shaders/RMSNormShader.cs:129-150) + MatrixMultiplyShader
+ *           (MatrixMultiplyShader.cs:266-288) + the host residual add (TransformerBlock.cs:151-161). */
+int nfai_op_gemv(nfai_ctx* ctx, const void* W, int dtype, uint32_t N, uint32_t K, const float* x, const float* gain,
+                 float eps, const float* resid, float* y);
+
+/* Fused Q/K/V projection of one token at position `pos`: a = RMSNorm(x); q = RoPE(Wq a) -> q_out[qH*d];
+ * K row = RoPE(Wk a), V row = Wv a written into row `pos` of kcache / vcache ([ctx][kvH*d] of kv_dtype).
+ * Wqkv is [qH*d + 2*kvH*d][H] (Q rows, then K rows, then V rows). rope_cs is [ctx][ropeDim/2] (cos, sin) pairs.
+ * replaces: attn RMSNorm + three MatrixMultiplyShader dispatches + two RoPEShader dispatches
+ *           (TransformerBlock.cs:129-141, NFAI.Vulkan.Shaders/RoPEShader.cs:238-271). */
+int nfai_op_qkv_rope(nfai_ctx* ctx, const void* Wqkv, int dtype, const float* x, const float* gain, float eps,
+                     uint32_t H, uint32_t qH, uint32_t kvH, uint32_t d, uint32_t ropeDim, const float* rope_cs,
+                     uint32_t pos, float* q_out, void* kcache, void* vcache, int kv_dtype);
+
+/* h = up * silu(gate) with gate = Wg a, up = Wu a, a = RMSNorm(x). Wgu is [2F][H] with gate row j at 2j and up
+ * row j at 2j+1.
+ * replaces: ffn RMSNorm + up/gate MatrixMultiplyShader + SiLUShader + ElementWiseMultiplicationShader
+ *           (TransformerBlock.cs:163-171, NFAI.Vulkan.Shaders/SiLUShader.cs:112-127,
+ *           NFAI.Vulkan.Shaders/ElementWiseMultiplicationShader.cs:127-138). */
+int nfai_op_ffn_gate_up(nfai_ctx* ctx, const void* Wgu, int dtype, const float* x, const float* gain, float eps,
+                        uint32_t H, uint32_t F, float* h_out);
+
+/* One new token's attention over positions 0..seq-1 of a position-major cache, all query heads:
+ * out[h*d+i] = sum_t softmax_t(q_h . K[t, h/(qH/kvH)] / sqrt(d)) * V[t, h/(qH/kvH), i].
+ * `scratch` is device memory for the split partial results; nfai_op_attn_scratch_bytes gives the size needed.
+ * replaces: AttentionScoreCalculationShader (NFAI.Vulkan.Shaders/AttentionScoreCalculationShader.cs:170-205),
+ *           AttentionSoftmaxShader (NFAI.Vulkan.Shaders/AttentionSoftmaxShader.cs:145-177) and
+ *           AttentionWeightedValueSumShader (NFAI.Vulkan.Shaders/AttentionWeightedValueSumShader.cs:181-215). */
+int nfai_op_attn_decode(nfai_ctx* ctx, const float* q, const void* kcache, const void* vcache, int kv_dtype,
+                        uint32_t seq, uint32_t qH, uint32_t kvH, uint32_t d, float* out, void* scratch,
+                        size_t scratch_bytes);
+size_t nfai_op_attn_scratch_bytes(uint32_t qH, uint32_t kvH, uint32_t d, uint32_t max_seq);
+
+/* logits = W * RMSNorm(x) (W[V][H]) and the lowest index of their maximum into *argmax_out (device).
+ * replaces: output RMSNorm + LM-head MatrixMultiplyShader (LlamaModel.cs:58-67,160-163) and
+ *           SamplingUtils.ArgMax (SamplingUtils.cs:55-56). */
+int nfai_op_lm_head(nfai_ctx* ctx, const void* W, int dtype, const float* x, const float* gain, float eps, uint32_t H,
+                    uint32_t V, float* logits, uint32_t* argmax_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NFAI_CUDA_H */

@@ -1,0 +1,350 @@
+// Batch-1 decode GEMV family: y = W * f(x) with fused prologue (RMSNorm) and epilogues (residual add,
+// RoPE + KV-cache write, SiLU*up, logits + arg-max partials).
+//
+// The work is HBM-bound (one FMA per 2 or 4 weight bytes), so the kernel is a weight streamer:
+//  * a warp owns R consecutive rows; its lanes walk each row in 16-byte vectors (8 halves / 4 floats), 512
+//    contiguous bytes per warp per row per step;
+//  * U steps are issued back to back and the next batch is requested before the current one is consumed, so
+//    every lane keeps 2*U*R 16-byte loads in flight;
+//  * the first batch is requested BEFORE the programmatic-dependency wait: the weights do not depend on the
+//    previous kernel, so they stream while it drains and while this CTA normalises x;
+//  * x (float32) sits in shared memory and is reused by all R rows of all warps; accumulation is float32;
+//  * the row sum is finished with warp shuffles; lane 0 applies the epilogue.
+// No tensor cores: with one right-hand side there is nothing for them to reuse.
+//
+// Reference arithmetic this replaces: NFAI.Vulkan.Shaders/MatrixMultiplyShader.cs:266-288 (one thread per
+// output, serial k loop), RMSNormShader.cs:129-150, RoPEShader.cs:238-271, SiLUShader.cs:112-127,
+// ElementWiseMultiplicationShader.cs:127-138, host residual adds at TransformerBlock.cs:151-161,174-181.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace nfai {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+// ---- prologue: x (optionally RMS-normalised) into shared memory ----------------------------------------------
+// ss = sum x^2 ; rms = sqrt(ss/K + eps) ; xs = (x / rms) * gain   (RMSNormShader.cs:136-148)
+__device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* red) {
+  const uint32_t K = p.K;
+  const int tid = threadIdx.x;
+  if (p.gain == nullptr) {
+    for (uint32_t i = tid; i < K; i += kThreads) xs[i] = p.x[i];
+    __syncthreads();
+    return;
+  }
+  float ss = 0.f;
+  for (uint32_t i = tid; i < K; i += kThreads) {
+    float v = p.x[i];
+    xs[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) tot += red[w];
+  const float rms = sqrtf(__fdiv_rn(tot, (float)K) + p.eps);
+  for (uint32_t i = tid; i < K; i += kThreads) xs[i] = __fmul_rn(__fdiv_rn(xs[i], rms), p.gain[i]);
+  __syncthreads();
+}
+
+// ---- epilogues (lane 0 of the warp holds the R finished row sums) ---------------------------------------------
+template <typename KVT, int R, int EPI>
+__device__ __forceinline__ void epilogue(const GemvParams& p, uint32_t row0, const float (&acc)[R], float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if constexpr (EPI == EPI_STORE) {
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        uint32_t n = row0 + r;
+        if (n < p.N) p.y[n] = p.resid ? p.resid[n] + acc[r] : acc[r];
+      }
+    }
+  } else if constexpr (EPI == EPI_QKV_ROPE) {
+    static_assert(R % 2 == 0, "RoPE pairs adjacent rows");
+    if (lane == 0) {
+      const uint32_t pos = p.state ? p.state->pos : p.pos_imm;
+      if (pos >= p.ctx) {
+        if (p.state) atomicOr(&p.state->err, 2u);
+        return;
+      }
+#pragma unroll
+      for (int r = 0; r < R; r += 2) {
+        uint32_t n = row0 + r;
+        if (n >= p.N) break;
+        float a = acc[r], b = acc[r + 1];
+        if (n < p.qDim + p.kvDim) {  // Q or K: rotate the pair (2m, 2m+1) of its head
+          uint32_t local = n < p.qDim ? n : n - p.qDim;
+          uint32_t i = local % p.d;
+          if (i < p.ropeDim) {
+            float2 cs = p.rope_cs[(size_t)pos * (p.ropeDim / 2) + (i >> 1)];
+            // value1 = cos*a - sin*b ; value2 = sin*a + cos*b (RoPEShader.cs:256-257), products rounded separately
+            float v1 = __fsub_rn(__fmul_rn(cs.x, a), __fmul_rn(cs.y, b));
+            float v2 = __fadd_rn(__fmul_rn(cs.y, a), __fmul_rn(cs.x, b));
+            a = v1;
+            b = v2;
+          }
+          if (n < p.qDim) {
+            p.q_out[n] = a;
+            p.q_out[n + 1] = b;
+          } else {
+            KVT* kc = reinterpret_cast<KVT*>(p.kcache) + (size_t)pos * p.kvDim + local;
+            store_as(kc, a);
+            store_as(kc + 1, b);
+          }
+        } else {
+          KVT* vc = reinterpret_cast<KVT*>(p.vcache) + (size_t)pos * p.kvDim + (n - p.qDim - p.kvDim);
+          store_as(vc, a);
+          store_as(vc + 1, b);
+        }
+      }
+    }
+  } else if constexpr (EPI == EPI_SILU_MUL) {
+    static_assert(R % 2 == 0, "gate and up rows are interleaved");
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < R; r += 2) {
+        uint32_t n = row0 + r;
+        if (n >= p.N) break;
+        float gate = acc[r], up = acc[r + 1];
+        // sigmoid = 1/(1+exp(-x)); silu = x*sigmoid; h = up*silu (SiLUShader.cs:121-123, ElementWiseMul A=up,B=silu)
+        float sig = __fdiv_rn(1.0f, 1.0f + expf(-gate));
+        p.y[n >> 1] = __fmul_rn(up, __fmul_rn(gate, sig));
+      }
+    }
+  } else {  // EPI_LOGITS
+    float bv = -INFINITY;
+    uint32_t bi = 0xffffffffu;
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        uint32_t n = row0 + r;
+        if (n < p.N) {
+          p.y[n] = acc[r];
+          if (bi == 0xffffffffu || acc[r] > bv) {
+            bv = acc[r];
+            bi = n;
+          }
+        }
+      }
+      red[warp] = bv;
+      reinterpret_cast<uint32_t*>(red)[kWarps + warp] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float v = red[0];
+      uint32_t ix = reinterpret_cast<uint32_t*>(red)[kWarps];
+      for (int w = 1; w < kWarps; ++w) {
+        float wv = red[w];
+        uint32_t wi = reinterpret_cast<uint32_t*>(red)[kWarps + w];
+        if (wi != 0xffffffffu && (ix == 0xffffffffu || wv > v)) {  // ascending rows: strict > keeps the lowest index
+          v = wv;
+          ix = wi;
+        }
+      }
+      p.part_val[blockIdx.x] = v;
+      p.part_idx[blockIdx.x] = ix;
+    }
+  }
+}
+
+// ---- the streamer ---------------------------------------------------------------------------------------------
+template <typename WT, typename KVT, int R, int U, int EPI>
+__global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
+  extern __shared__ __align__(16) float smem[];
+  float* red = smem;       // 2*kWarps words of reduction scratch
+  float* xs = smem + 32;   // K floats
+  constexpr int VE = WeightVec<WT>::kElems;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t row0 = (blockIdx.x * kWarps + warp) * R;
+  const uint32_t nvec = p.K / VE;  // host guarantees K % VE == 0 and 16-byte aligned rows
+  const uint4* wrow[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    uint32_t n = row0 + r < p.N ? row0 + r : p.N - 1;  // clamp: tail warps re-read the last row, never out of bounds
+    wrow[r] = reinterpret_cast<const uint4*>(reinterpret_cast<const WT*>(p.W) + (size_t)n * p.K);
+  }
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  uint4 cur[U][R];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    uint32_t v = lane + 32 * u;
+#pragma unroll
+    for (int r = 0; r < R; ++r) cur[u][r] = v < nvec ? ld_stream16(wrow[r] + v) : zero;
+  }
+  pdl_launch_dependents();
+  pdl_wait();
+  load_x(p, xs, red);
+
+  float acc[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r] = 0.f;
+  for (uint32_t base = 0; base < nvec; base += 32 * U) {
+    uint4 nxt[U][R];
+    const uint32_t nb = base + 32 * U;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      uint32_t v = nb + lane + 32 * u;
+#pragma unroll
+      for (int r = 0; r < R; ++r) nxt[u][r] = v < nvec ? ld_stream16(wrow[r] + v) : zero;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      uint32_t v = base + lane + 32 * u;
+      if (v < nvec) {
+        float xv[VE];
+        const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)v * VE);
+#pragma unroll
+        for (int i = 0; i < VE / 4; ++i) {
+          float4 t = xp[i];
+          xv[4 * i] = t.x;
+          xv[4 * i + 1] = t.y;
+          xv[4 * i + 2] = t.z;
+          xv[4 * i + 3] = t.w;
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          float wf[VE];
+          WeightVec<WT>::unpack(cur[u][r], wf);
+#pragma unroll
+          for (int i = 0; i < VE; ++i) acc[r] = fmaf(wf[i], xv[i], acc[r]);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int r = 0; r < R; ++r) cur[u][r] = nxt[u][r];
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r] = warp_sum(acc[r]);
+  epilogue<KVT, R, EPI>(p, row0, acc, red);
+}
+
+// Same contract for any K and any alignment (element loads); used when K is not a multiple of the vector width.
+template <typename WT, typename KVT, int EPI>
+__global__ void __launch_bounds__(kThreads) gemv_scalar_kernel(const GemvParams p) {
+  extern __shared__ __align__(16) float smem[];
+  float* red = smem;
+  float* xs = smem + 32;
+  constexpr int R = 2;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t row0 = (blockIdx.x * kWarps + warp) * R;
+  pdl_launch_dependents();
+  pdl_wait();
+  load_x(p, xs, red);
+  float acc[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    uint32_t n = row0 + r < p.N ? row0 + r : p.N - 1;
+    const WT* w = reinterpret_cast<const WT*>(p.W) + (size_t)n * p.K;
+    float a = 0.f;
+    for (uint32_t k = lane; k < p.K; k += 32) a = fmaf(to_float(w[k]), xs[k], a);
+    acc[r] = warp_sum(a);
+  }
+  epilogue<KVT, R, EPI>(p, row0, acc, red);
+}
+
+template <typename K>
+cudaError_t launch_k(K kernel, dim3 grid, size_t smem, cudaStream_t s, bool pdl, const GemvParams& p) {
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
+template <typename WT, typename KVT, int R, int EPI>
+cudaError_t launch_u(int U, dim3 grid, size_t smem, cudaStream_t s, bool pdl, const GemvParams& p) {
+  switch (U) {
+    case 2: return launch_k(gemv_kernel<WT, KVT, R, 2, EPI>, grid, smem, s, pdl, p);
+    case 4: return launch_k(gemv_kernel<WT, KVT, R, 4, EPI>, grid, smem, s, pdl, p);
+    case 8:
+      if constexpr (R <= 2) return launch_k(gemv_kernel<WT, KVT, R, 8, EPI>, grid, smem, s, pdl, p);
+      return cudaErrorInvalidValue;  // 4 rows x 8 steps x 2 buffers would not fit the register file
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+template <typename WT, typename KVT, int EPI>
+cudaError_t launch_r(int R, int U, dim3 grid, size_t smem, cudaStream_t s, bool pdl, const GemvParams& p) {
+  if constexpr (EPI == EPI_STORE || EPI == EPI_LOGITS) {
+    if (R == 1) return launch_u<WT, KVT, 1, EPI>(U, grid, smem, s, pdl, p);
+  }
+  if (R == 2) return launch_u<WT, KVT, 2, EPI>(U, grid, smem, s, pdl, p);
+  if (R == 4) return launch_u<WT, KVT, 4, EPI>(U, grid, smem, s, pdl, p);
+  return cudaErrorInvalidValue;
+}
+
+template <typename WT, typename KVT>
+cudaError_t launch_e(GemvEpilogue epi, bool vec, int R, int U, dim3 grid, size_t smem, cudaStream_t s, bool pdl,
+                     const GemvParams& p) {
+  if (!vec) {
+    switch (epi) {
+      case EPI_STORE: return launch_k(gemv_scalar_kernel<WT, float, EPI_STORE>, grid, smem, s, pdl, p);
+      case EPI_QKV_ROPE: return launch_k(gemv_scalar_kernel<WT, KVT, EPI_QKV_ROPE>, grid, smem, s, pdl, p);
+      case EPI_SILU_MUL: return launch_k(gemv_scalar_kernel<WT, float, EPI_SILU_MUL>, grid, smem, s, pdl, p);
+      case EPI_LOGITS: return launch_k(gemv_scalar_kernel<WT, float, EPI_LOGITS>, grid, smem, s, pdl, p);
+    }
+    return cudaErrorInvalidValue;
+  }
+  switch (epi) {
+    case EPI_STORE: return launch_r<WT, float, EPI_STORE>(R, U, grid, smem, s, pdl, p);
+    case EPI_QKV_ROPE: return launch_r<WT, KVT, EPI_QKV_ROPE>(R, U, grid, smem, s, pdl, p);
+    case EPI_SILU_MUL: return launch_r<WT, float, EPI_SILU_MUL>(R, U, grid, smem, s, pdl, p);
+    case EPI_LOGITS: return launch_r<WT, float, EPI_LOGITS>(R, U, grid, smem, s, pdl, p);
+  }
+  return cudaErrorInvalidValue;
+}
+
+bool vector_ok(int wdtype, const GemvParams& p) {
+  const uint32_t ve = wdtype == 1 ? 8 : 4;
+  return p.K % ve == 0 && (reinterpret_cast<uintptr_t>(p.W) & 15) == 0;
+}
+
+int rows_per_warp(GemvEpilogue epi, bool vec, const GemvTune& t) {
+  if (!vec) return 2;
+  int R = t.rows_per_warp;
+  if ((epi == EPI_QKV_ROPE || epi == EPI_SILU_MUL) && R < 2) R = 2;
+  return R;
+}
+
+}  // namespace
+
+uint32_t gemv_grid(int wdtype, GemvEpilogue epi, const GemvParams& p, const GemvTune& t) {
+  const uint32_t per_cta = kWarps * rows_per_warp(epi, vector_ok(wdtype, p), t);
+  return (p.N + per_cta - 1) / per_cta;
+}
+
+cudaError_t launch_gemv(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue epi, const GemvParams& p,
+                        const GemvTune& t, bool pdl) {
+  if (p.N == 0 || p.K == 0) return cudaErrorInvalidValue;
+  if ((epi == EPI_QKV_ROPE || epi == EPI_SILU_MUL) && (p.N % 2) != 0) return cudaErrorInvalidValue;
+  const bool vec = vector_ok(wdtype, p);
+  const int R = rows_per_warp(epi, vec, t);
+  dim3 grid(gemv_grid(wdtype, epi, p, t));
+  size_t smem = (32 + (size_t)p.K) * sizeof(float);
+  if (smem > 227 * 1024) return cudaErrorInvalidValue;
+  if (wdtype == 1) {
+    if (kvdtype == 1) return launch_e<__half, __half>(epi, vec, R, t.unroll, grid, smem, s, pdl, p);
+    return launch_e<__half, float>(epi, vec, R, t.unroll, grid, smem, s, pdl, p);
+  }
+  if (kvdtype == 1) return launch_e<float, __half>(epi, vec, R, t.unroll, grid, smem, s, pdl, p);
+  return launch_e<float, float>(epi, vec, R, t.unroll, grid, smem, s, pdl, p);
+}
+
+}  // namespace nfai

@@ -1,0 +1,104 @@
+// Host-side launch interface of the kernels in libnfai_cuda (internal; the public ABI is include/nfai_cuda.h).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace nfai {
+
+// Device-resident state of one model: the graph's kernels read and advance it so that one captured graph
+// serves every position.
+struct StepState {
+  uint32_t pos;         // number of tokens already in the KV cache = position of the token being processed
+  uint32_t cur_token;   // token the next decode step embeds (the final kernel feeds the arg-max back here)
+  uint32_t prompt_idx;  // cursor into the prompt buffer for head-less prompt steps
+  uint32_t last_argmax; // arg-max of the last step that ran the LM head
+  uint32_t err;         // sticky error bits: 1 = token id out of range, 2 = position beyond the cache
+  uint32_t steps;       // number of steps executed (diagnostics)
+  uint32_t pad[2];
+};
+
+enum GemvEpilogue {
+  EPI_STORE = 0,     // y = acc (+ resid)
+  EPI_QKV_ROPE = 1,  // rows are [Q | K | V]; RoPE on Q and K; K,V rows go to the cache at row pos
+  EPI_SILU_MUL = 2,  // rows are interleaved (gate_j, up_j); h_j = up_j * silu(gate_j)
+  EPI_LOGITS = 3     // y = acc and a per-CTA (max, lowest index) partial
+};
+
+struct GemvParams {
+  const void* W = nullptr;  // [N][K] row-major, float or half
+  uint32_t N = 0, K = 0;
+  const float* x = nullptr;     // [K]
+  const float* gain = nullptr;  // [K] RMSNorm gain, or null for no normalisation
+  float eps = 0.f;
+  const float* resid = nullptr;  // [N] or null
+  float* y = nullptr;            // [N] (EPI_STORE, EPI_LOGITS) or [N/2] (EPI_SILU_MUL)
+  // EPI_QKV_ROPE
+  float* q_out = nullptr;
+  void* kcache = nullptr;  // [ctx][kvDim] of the kv type
+  void* vcache = nullptr;
+  uint32_t qDim = 0, kvDim = 0, d = 0, ropeDim = 0, ctx = 0;
+  const float2* rope_cs = nullptr;  // [ctx][ropeDim/2] (cos, sin)
+  // position: *state (if non-null) else pos_imm
+  StepState* state = nullptr;
+  uint32_t pos_imm = 0;
+  // EPI_LOGITS
+  float* part_val = nullptr;
+  uint32_t* part_idx = nullptr;
+};
+
+// Tunable launch shape of the GEMV family.
+struct GemvTune {
+  int rows_per_warp = 2;  // 1, 2 or 4 (EPI_QKV_ROPE and EPI_SILU_MUL need an even value)
+  int unroll = 4;         // 16-byte loads in flight per row per lane: 2, 4 or 8
+};
+
+// Number of CTAs the launch will use (the LM head needs it to size its partial buffers).
+uint32_t gemv_grid(int wdtype, GemvEpilogue epi, const GemvParams& p, const GemvTune& t);
+cudaError_t launch_gemv(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue epi, const GemvParams& p,
+                        const GemvTune& t, bool pdl);
+
+struct AttnParams {
+  const float* q = nullptr;  // [qH*d], rotated
+  const void* kcache = nullptr;
+  const void* vcache = nullptr;  // [ctx][kvH*d]
+  uint32_t qH = 0, kvH = 0, d = 0;
+  StepState* state = nullptr;  // seq = state->pos + 1 when non-null
+  uint32_t seq_imm = 0;
+  float* out = nullptr;        // [qH*d]
+  float* part = nullptr;       // [qH][S_max][d+2] split partials
+  uint32_t* tickets = nullptr; // [kvH * head_groups], zero between launches
+  uint32_t S_max = 1;
+};
+
+constexpr uint32_t kAttnTile = 32;       // positions per tile
+constexpr uint32_t kAttnHeadsPerCta = 4;  // query heads sharing one pass over K/V
+
+uint32_t attn_head_groups(uint32_t qH, uint32_t kvH);
+uint32_t attn_splits(uint32_t qH, uint32_t kvH, uint32_t max_seq);
+size_t attn_part_floats(uint32_t qH, uint32_t d, uint32_t S_max);
+cudaError_t launch_attn_decode(cudaStream_t s, int kvdtype, const AttnParams& p, bool pdl);
+
+cudaError_t launch_embed(cudaStream_t s, int wdtype, const void* E, uint32_t H, uint32_t V, StepState* state,
+                         const uint32_t* prompt, uint32_t token_imm, float* x_out, bool pdl);
+// Reduce the LM head's per-CTA partials to the arg-max (lowest index among maxima), feed it back as the next
+// token and advance the position.
+cudaError_t launch_argmax_final(cudaStream_t s, const float* part_val, const uint32_t* part_idx, uint32_t nparts,
+                                StepState* state, uint32_t* argmax_out, uint32_t* history, uint32_t history_cap,
+                                bool pdl);
+// Head-less prompt step: position and prompt cursor advance by one.
+cudaError_t launch_advance(cudaStream_t s, StepState* state, bool pdl);
+
+// Scatter/convert one uploaded chunk into a matrix's final place: source element g = elem_off + e sits at
+// (row, col) = (g / K, g % K); rows [row_lo,row_hi) x cols [col_lo,col_hi) are kept and land at
+// dst[((row-row_lo)*row_mul + row_off) * ldd + (col-col_lo)].
+struct IngestParams {
+  const void* src = nullptr;
+  uint64_t n = 0, elem_off = 0, K = 1;
+  uint64_t row_lo = 0, row_hi = 0, col_lo = 0, col_hi = 0;
+  uint64_t row_mul = 1, row_off = 0, ldd = 0;
+  void* dst = nullptr;
+};
+cudaError_t launch_ingest(cudaStream_t s, int src_dtype, int dst_dtype, const IngestParams& p);
+
+}  // namespace nfai

@@ -1,0 +1,33 @@
+// Tensor-parallel exchange steps of the decode path (internal). NCCL is loaded at run time with dlopen so that
+// single-GPU use needs no NCCL at all.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include <string>
+
+namespace nfai {
+
+struct TpComm;
+
+int tp_unique_id(void* out, size_t out_bytes, std::string& err);
+int tp_create(TpComm** out, int device, int rank, int world, const void* uid, size_t uid_bytes, cudaStream_t s,
+              std::string& err);
+void tp_destroy(TpComm* tp);
+
+// buf[0..H) holds this rank's partial sums; afterwards x_out = resid + sum over ranks (identical on every rank).
+// *launches is advanced by the number of kernels of this library that were enqueued.
+cudaError_t tp_allreduce_residual(TpComm* tp, cudaStream_t s, float* buf, const float* resid, float* x_out, uint32_t H,
+                                  int* launches);
+
+// part_val/part_idx hold nparts per-CTA arg-max partials with rank-local row indices; afterwards entries
+// [0, world) hold one (max, global lowest index) pair per rank, on every rank.
+cudaError_t tp_gather_argmax(TpComm* tp, cudaStream_t s, float* part_val, uint32_t* part_idx, uint32_t nparts,
+                             uint32_t v_lo, int* launches);
+
+// All ranks' logits shards, in rank order, into pinned host memory (V = world * Vl floats).
+int tp_allgather_logits(TpComm* tp, cudaStream_t s, const float* logits_local, uint32_t Vl, float* host_out,
+                        std::string& err);
+
+}  // namespace nfai

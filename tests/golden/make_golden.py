@@ -1,0 +1,67 @@
+"""Generate the golden fixtures in this directory from the CPU oracle.
+
+    python tests/golden/make_golden.py
+
+The reference has no golden vectors for this path and cannot run here, so these fixtures pin the ORACLE
+(float32, sequential order) on seeded synthetic models: they catch any later drift of the oracle, of the model
+generator and of the CUDA path. Each .npz holds, for one configuration: the prompt, the teacher-forced logits
+at a few prompt positions, the arg-max of every prompt position and the greedy continuation.
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from nfai_b200 import synth  # noqa: E402
+from oracle import oracle as O  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+# key -> (config key, overrides, prompt length, greedy steps, positions whose logits are stored)
+CASES = {
+    "c0": ("c0", {}, 64, 64, [0, 1, 31, 63]),
+    "c0p": ("c0p", {}, 64, 64, [0, 63]),
+    "c0_gain": ("c0", {"gain_std": 0.1}, 16, 16, [0, 15]),
+    "s3_f16_untied": ("s3", {"gain_std": 0.1}, 24, 16, [0, 23]),
+    "s2_f16_d128": ("s2", {}, 16, 8, [15]),
+}
+
+
+def make(key: str):
+    cfg_key, over, n_prompt, n_greedy, keep = CASES[key]
+    cfg = synth.get_config(cfg_key, **over)
+    m = O.OracleModel(cfg, ctx=n_prompt + n_greedy).load_synthetic(0)
+    prompt = synth.prompt_ids(cfg, n_prompt, 0)
+    kept, argmaxes = [], []
+    logits = None
+    for i, t in enumerate(prompt):
+        logits = m.decode(int(t))
+        argmaxes.append(O.argmax(logits))
+        if i in keep:
+            kept.append(logits.copy())
+    greedy = []
+    tk = argmaxes[-1]
+    greedy.append(tk)
+    greedy_logits_last = None
+    while len(greedy) < n_greedy:
+        greedy_logits_last = m.decode(tk)
+        tk = O.argmax(greedy_logits_last)
+        greedy.append(tk)
+    np.savez_compressed(
+        os.path.join(HERE, f"{key}.npz"),
+        prompt=prompt.astype(np.uint32),
+        keep=np.array(keep, np.int32),
+        logits=np.stack(kept).astype(np.float32),
+        prompt_argmax=np.array(argmaxes, np.uint32),
+        greedy=np.array(greedy, np.uint32),
+        greedy_logits_last=greedy_logits_last.astype(np.float32),
+    )
+    print(key, "greedy head:", greedy[:8])
+
+
+if __name__ == "__main__":
+    for k in CASES:
+        make(k)
