@@ -1,0 +1,308 @@
+"""Benchmark of the Llama-3 batch-1 decode path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c1]
+
+A step is one decoded token (one replay of the captured decode step). At N = 1 the workload is the
+Llama-3.2-1B-architecture FP16 model, 128-token random prompt, then K greedy decode steps; for N > 1 the same
+model runs tensor-parallel over the N GPUs (strong scaling), one rank per GPU under torchrun.
+Prints ONE JSON line on rank 0.
+
+  value      tokens/s with everything resident in HBM: K greedy steps fed back on the device, timed with CUDA events
+             on the library's stream, max over ranks.
+  e2e        tokens/s through the reference-facing call (nfai_decode): host token in, arg-max out, copies and
+             synchronisation inside the timed region.
+  roofline   the dominant kernel (FFN gate/up GEMV): algorithmic bytes per launch / mean launch time, against the
+             measured HBM copy bandwidth.
+  cpu_baseline  the CPU oracle (a port of the reference's arithmetic; the reference itself needs .NET + Vulkan and
+             cannot run here) timed on the host cores on a few tokens of the same workload.
+
+--impl reference times that CPU port with all host threads on the same workload (rank 0 only).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0
+PROMPT_LEN = 128
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 9:
+                self.rows.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_baseline(cfg, threads: int, tokens: int, seed: int = 0):
+    """Time `tokens` decode steps of the CPU oracle at positions PROMPT_LEN.. (cache rows below are zero-filled;
+    the arithmetic and the bytes moved are those of the real workload)."""
+    from oracle import oracle as O
+    m = O.OracleModel(cfg, ctx=PROMPT_LEN + tokens + 2).load_synthetic(seed)
+    O.set_threads(threads)
+    m.set_position(PROMPT_LEN)
+    m.decode(1)  # warm-up token (page in the weights)
+    t0 = time.perf_counter()
+    tk = 1
+    for _ in range(tokens):
+        tk = O.argmax(m.decode(tk))
+    dt = time.perf_counter() - t0
+    m.close()
+    return tokens / dt, dt / tokens
+
+
+def workload_name(cfg_key: str, cfg, steps: int) -> str:
+    label = f"configs[{cfg_key[1:]}]" if cfg_key[0] == "c" else cfg_key
+    return (f"{label}: {cfg.name} batch 1, {PROMPT_LEN}-token uniform-random prompt, "
+            f"{steps} greedy decode steps")
+
+
+def run_reference(args, cfg):
+    """The reference's arithmetic on the host cores (CPU port; the reference's own Vulkan path is unavailable)."""
+    from oracle import oracle as O
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    O.set_threads(threads)
+    m = O.OracleModel(cfg, ctx=PROMPT_LEN + args.warmup + args.steps + 2).load_synthetic(args.seed)
+    m.set_position(PROMPT_LEN)
+    tk = 1
+    t_w = time.perf_counter()
+    for _ in range(max(1, args.warmup)):
+        tk = O.argmax(m.decode(tk))
+    per_tok = (time.perf_counter() - t_w) / max(1, args.warmup)
+    budget_s = 150.0
+    steps = max(1, min(args.steps, int(budget_s / max(per_tok, 1e-6))))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tk = O.argmax(m.decode(tk))
+    dt = time.perf_counter() - t0
+    val = steps / dt
+    sample = f"{steps} decode steps at positions {PROMPT_LEN + max(1, args.warmup)}.. of the same model (KV rows below are zero-filled)"
+    line = {
+        "impl": "reference", "metric": "decode tok/s (batch 1)", "value": val, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": dt / steps * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args.config, cfg, args.steps), "weights": cfg.dtype,
+                   "note": "CPU port of the reference's shader arithmetic; the reference's Vulkan path (GPU or lavapipe) is unavailable on this box"},
+        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, cfg):
+    import torch
+
+    from nfai_b200 import LlamaModel, LlamaModelFactory, synth, synthetic_tensors
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    uid = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        from nfai_b200 import CudaContext
+        buf = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            buf.copy_(torch.frombuffer(bytearray(CudaContext.tp_unique_id()), dtype=torch.uint8))
+        dist.broadcast(buf, 0)
+        uid = bytes(buf.cpu().numpy().tobytes())
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    K, W = args.steps, max(args.warmup, 3)
+    ctx_size = PROMPT_LEN + W + K + 8
+    factory = LlamaModelFactory(local_rank, rank, world, uid)
+    t_load = time.perf_counter()
+    model = LlamaModel(factory.ctx, synth.metadata(cfg), synthetic_tensors(cfg, args.seed), ctx_size,
+                       kv_dtype=args.kv_dtype)
+    load_s = time.perf_counter() - t_load
+    prompt = synth.prompt_ids(cfg, PROMPT_LEN, args.seed)
+    barrier()
+    t_pf = time.perf_counter()
+    _, am = model.prefill(prompt, want_logits=False)
+    barrier()
+    prefill_s = time.perf_counter() - t_pf
+
+    # ---- value: device-resident greedy decode, CUDA events on the library's stream
+    toks_w, _ = model.decode_greedy(am, W)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    toks, ms = model.decode_greedy(int(toks_w[-1]), K)
+    barrier()
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+
+    # ---- e2e: the reference-facing call per token, host token in / arg-max out
+    model.set_position(PROMPT_LEN)
+    tk = am
+    for _ in range(W):
+        _, tk = model.decode(tk, want_logits=False)
+    barrier()
+    t0 = time.perf_counter()
+    e2e_toks = []
+    for _ in range(K):
+        _, tk = model.decode(tk, want_logits=False)
+        e2e_toks.append(tk)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_s = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    same_tokens = list(toks) == e2e_toks
+
+    # ---- roofline of the dominant kernel, timed alone with events on the same stream
+    peak, peak_kind = measured_peak()
+    kern = {}
+    for name in ("ffn_gate_up", "ffn_down", "qkv_rope", "attn_out", "lm_head", "attention"):
+        kms, kbytes = model.profile_kernel(name, 64 if name != "lm_head" else 16)
+        kern[name] = {"us": kms * 1e3, "bytes": kbytes, "gbs": kbytes / (kms * 1e-3) / 1e9}
+    launches = model.step_launches()
+    kv_bytes = 2 if model.kv_dtype == "f16" else 4
+    first_pos = PROMPT_LEN + W
+    step_bytes = sum(synth.decode_bytes(cfg, p, kv_bytes) for p in range(first_pos, first_pos + K)) / K / world
+    model.Dispose()
+    factory.Dispose()
+    if rank != 0:
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    dom = kern["ffn_gate_up"]
+    value = K / (ms * 1e-3)
+    line = {
+        "metric": "decode tok/s (batch 1)", "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32 accumulate over " + cfg.dtype + " weights", "data": "synthetic",
+        "config": {"workload": workload_name(args.config, cfg, K), "weights": cfg.dtype, "kv_cache": model.kv_dtype,
+                   "parallelism": f"tp{world}", "l2": "inputs larger than L2: every step streams all weights "
+                   f"({cfg.streamed_matrix_params() * 2 / 1e9:.2f} GB at TP1) against a 126 MB L2",
+                   "seed": args.seed},
+        "e2e": {"value": K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 32,
+                "same_tokens_as_device_loop": same_tokens},
+        "gpu_launches": K * launches,
+        "roofline": {"bound": "hbm", "kernel": "gemv_kernel (FFN gate/up + RMSNorm + SiLU*up)", "achieved": dom["gbs"],
+                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": None,
+                     "launch_us": dom["us"], "bytes_per_launch": dom["bytes"]},
+        "step_roofline": {"bytes_per_token_per_gpu": step_bytes, "achieved_gbs": step_bytes / (ms / K * 1e-3) / 1e9,
+                          "frac_of_8tbs": step_bytes / (ms / K * 1e-3) / 8e12,
+                          "frac_of_measured": step_bytes / (ms / K * 1e-3) / 1e9 / peak},
+        "kernels": kern,
+        "clocks": clocks,
+        "load_s": load_s, "prefill_tok_s": PROMPT_LEN / prefill_s,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        n_tok = 8
+        v, s_per = cpu_baseline(cfg, threads, n_tok, args.seed)
+        line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": threads, "kind": "port",
+                                "sample": f"{n_tok} decode steps at positions {PROMPT_LEN + 1}.. of the same model "
+                                          "(KV rows below are zero-filled), all host threads"}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="c1", choices=["c0", "c1", "c2", "c3", "s1"])
+    ap.add_argument("--kv-dtype", default="f16", choices=["f16", "f32", "auto"])
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    from nfai_b200 import synth
+    cfg = synth.get_config(args.config)
+    if args.impl == "reference":
+        run_reference(args, cfg)
+    else:
+        run_ours(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

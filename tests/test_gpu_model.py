@@ -1,0 +1,236 @@
+"""Whole-path parity through the reference-facing interface (LlamaModel over the C ABI) against the CPU oracle.
+
+Tolerances (from the path's specification): float32 model logits max|a-b|/max|b| <= 1e-4; float16 models
+max|a-b| <= 2e-2; greedy token sequences identical on the tiny float32 configuration; embedding rows and arg-max
+indices bit-exact.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from nfai_b200 import LlamaModelFactory, ModelOptions, NfaiError, Parser, _lib, create_synthetic_model, gguf_io, synth
+
+from .gpu_util import rel_err
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+REL_F32 = 1e-4
+ABS_F16 = 2e-2
+
+
+@pytest.fixture(scope="module")
+def factory():
+    f = LlamaModelFactory(0)
+    yield f
+    f.Dispose()
+
+
+def make(cfg, ctx, factory, **kw):
+    return create_synthetic_model(cfg, ctx, factory=factory, **kw)
+
+
+def check_logits(cfg, got, want):
+    if cfg.dtype == "f32":
+        assert rel_err(got, want) <= REL_F32
+    else:
+        assert float(np.abs(got - want).max()) <= ABS_F16
+
+
+@pytest.mark.parametrize("key,over", [("c0", {}), ("c0p", {}), ("c0", {"gain_std": 0.1}), ("s3", {"gain_std": 0.1}),
+                                      ("s2", {}), ("s1", {})])
+def test_teacher_forced_logits_and_taps(factory, oracle, key, over):
+    cfg = synth.get_config(key, **over)
+    n = 24 if key != "s1" else 8
+    toks = synth.prompt_ids(cfg, n, 0)
+    ref = oracle.OracleModel(cfg, ctx=n).load_synthetic(0)
+    m = make(cfg, n, factory, kv_dtype="f32")
+    for i, t in enumerate(toks):
+        want = ref.decode(int(t))
+        got, am = m.decode(int(t))
+        check_logits(cfg, got, want)
+        assert am == oracle.argmax(got)  # bit-exact index on the device's own logits
+        assert m.position == i + 1
+        if i in (0, n - 1):
+            for l in range(cfg.L):
+                assert rel_err(m.read_hidden(l), ref.read_hidden(l)) <= 1e-4
+                k, v = m.read_kv(l, i)
+                kr, vr = ref.read_kv(l, i)
+                assert rel_err(k, kr) <= 1e-4 and rel_err(v, vr) <= 1e-4
+    m.Dispose()
+
+
+def test_config0_prefill_and_64_greedy_tokens_match(factory, oracle):
+    g = np.load(os.path.join(GOLDEN, "c0.npz"))
+    cfg = synth.get_config("c0")
+    m = make(cfg, 128, factory)
+    logits, am = m.prefill(g["prompt"])
+    assert rel_err(logits, g["logits"][-1]) <= REL_F32
+    assert am == int(g["prompt_argmax"][-1]) == int(g["greedy"][0])
+    toks, ms = m.decode_greedy(am, 63)
+    assert list(toks) == list(g["greedy"][1:])
+    assert ms > 0
+    # the same through the host-driven loop (RunAsync with token ids)
+    m.reset()
+    assert m.run_tokens(g["prompt"], 64) == list(g["greedy"])
+    m.Dispose()
+
+
+@pytest.mark.parametrize("key", ["c0p", "c0_gain", "s3_f16_untied", "s2_f16_d128"])
+def test_golden_fixtures(factory, key):
+    from tests.golden.make_golden import CASES
+    cfg_key, over, n_prompt, n_greedy, keep = CASES[key]
+    g = np.load(os.path.join(GOLDEN, f"{key}.npz"))
+    cfg = synth.get_config(cfg_key, **over)
+    m = make(cfg, n_prompt + n_greedy, factory, kv_dtype="f32")
+    j = 0
+    for i, t in enumerate(g["prompt"]):
+        got, am = m.decode(int(t))
+        if i in keep:
+            check_logits(cfg, got, g["logits"][j])
+            j += 1
+    toks, _ = m.decode_greedy(am, n_greedy - 1)
+    if cfg.dtype == "f32":
+        assert am == int(g["greedy"][0]) and list(toks) == list(g["greedy"][1:])
+    m.Dispose()
+
+
+def test_prefill_equals_token_by_token(factory):
+    cfg = synth.get_config("s3", gain_std=0.1)
+    toks = synth.prompt_ids(cfg, 40, 1)
+    a = make(cfg, 64, factory)
+    b = make(cfg, 64, factory)
+    la, ama = a.prefill(toks)
+    for t in toks:
+        lb, amb = b.decode(int(t))
+    assert float(np.abs(la - lb).max()) <= 1e-5 and ama == amb
+    for l in range(cfg.L):
+        for p in (0, 17, 39):
+            ka, va = a.read_kv(l, p)
+            kb, vb = b.read_kv(l, p)
+            assert np.allclose(ka, kb, atol=1e-5) and np.allclose(va, vb, atol=1e-5)
+    # prompt in two pieces continues at the next position
+    a.reset()
+    a.prefill(toks[:13], want_logits=False)
+    lc, amc = a.prefill(toks[13:])
+    assert float(np.abs(lc - lb).max()) <= 1e-5 and amc == amb
+    a.Dispose()
+    b.Dispose()
+
+
+def test_fp16_kv_cache_stays_inside_the_fp16_bound(factory, oracle):
+    cfg = synth.get_config("s1")
+    toks = synth.prompt_ids(cfg, 12, 0)
+    ref = oracle.OracleModel(cfg, ctx=12).load_synthetic(0)
+    m = make(cfg, 12, factory, kv_dtype="f16")
+    for t in toks:
+        want = ref.decode(int(t))
+        got, _ = m.decode(int(t))
+        assert float(np.abs(got - want).max()) <= ABS_F16
+    m.Dispose()
+
+
+def test_widened_upload_equals_raw_half_upload(factory):
+    """Chunks widened to float32 (what the reference's GetDataRaw yields) narrow back exactly on the device."""
+    cfg = synth.get_config("s3")
+    toks = synth.prompt_ids(cfg, 6, 0)
+    a = make(cfg, 8, factory)
+    b = make(cfg, 8, factory, widen_half=True)
+    la, _ = a.prefill(toks)
+    lb, _ = b.prefill(toks)
+    assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+    a.Dispose()
+    b.Dispose()
+
+
+def test_gguf_file_through_parser(factory, oracle, tmp_path):
+    cfg = synth.get_config("c0p", gain_std=0.1)
+    path = os.path.join(tmp_path, "m.gguf")
+    gguf_io.write_synthetic_gguf(cfg, path, seed=2)
+    model = Parser([factory]).parse(ModelOptions(GGUFPath=path, KVCacheSize=16))
+    assert model.ModelName == cfg.name
+    ref = oracle.OracleModel(cfg, ctx=16).load_synthetic(2)
+    toks = synth.prompt_ids(cfg, 8, 2)
+    for t in toks:
+        want = ref.decode(int(t))
+        got, _ = model.decode(int(t))
+        assert rel_err(got, want) <= REL_F32
+    model.Dispose()
+
+
+def test_errors_are_statuses(factory):
+    cfg = synth.get_config("c0")
+    m = make(cfg, 4, factory)
+    with pytest.raises(NfaiError) as e:
+        m.decode(cfg.V)
+    assert e.value.code == _lib.ERR_ARG
+    m.prefill([1, 2, 3], want_logits=False)
+    with pytest.raises(NfaiError) as e:
+        m.prefill([1, 2], want_logits=False)
+    assert e.value.code == _lib.ERR_CONTEXT_FULL
+    m.decode(4, want_logits=False)
+    with pytest.raises(NfaiError) as e:
+        m.decode(5)
+    assert e.value.code == _lib.ERR_CONTEXT_FULL
+    assert m.position == 4
+    with pytest.raises(NfaiError) as e:
+        m.decode_greedy(1, 1)
+    assert e.value.code == _lib.ERR_CONTEXT_FULL
+    m.reset()
+    assert m.position == 0
+    m.decode(1)
+    m.Dispose()
+
+
+def test_upload_state_machine(factory):
+    import ctypes as C
+    lib = _lib.load()
+    cfg = synth.get_config("c0")
+    hp = _lib.HParams(cfg.H, cfg.L, cfg.qH, cfg.kvH, cfg.d, cfg.ropeDim, cfg.F, cfg.V, 8, cfg.eps, cfg.rope_theta,
+                      _lib.F32, _lib.F32, 1)
+    h = C.c_void_p()
+    _lib.check(lib.nfai_model_create(factory.ctx.handle, C.byref(hp), C.byref(h)), factory.ctx.handle)
+    shape = (C.c_uint64 * 2)(cfg.H, cfg.qDim)
+    assert lib.nfai_model_tensor_chunk(h, b"\0" * 16, 16) == _lib.ERR_STATE
+    assert lib.nfai_model_tensor_begin(h, b"blk.0.nonsense.weight", _lib.F32, shape, 2) == _lib.ERR_ARG
+    assert lib.nfai_model_tensor_begin(h, b"blk.9.attn_q.weight", _lib.F32, shape, 2) == _lib.ERR_ARG
+    bad = (C.c_uint64 * 2)(cfg.H + 1, cfg.qDim)
+    assert lib.nfai_model_tensor_begin(h, b"blk.0.attn_q.weight", _lib.F32, bad, 2) == _lib.ERR_ARG
+    assert lib.nfai_model_tensor_begin(h, b"blk.0.attn_q.weight", 7, shape, 2) == _lib.ERR_ARG
+    assert lib.nfai_model_tensor_begin(h, b"blk.0.attn_q.weight", _lib.F32, shape, 2) == _lib.OK
+    assert lib.nfai_model_tensor_begin(h, b"blk.0.attn_k.weight", _lib.F32, shape, 2) == _lib.ERR_STATE
+    assert lib.nfai_model_tensor_chunk(h, b"\0" * 6, 6) == _lib.ERR_ARG       # not a whole number of elements
+    assert lib.nfai_model_tensor_chunk(h, b"\0" * 64, 64) == _lib.OK
+    assert lib.nfai_model_tensor_end(h) == _lib.ERR_ARG                        # too few bytes
+    assert lib.nfai_model_finalize(h) == _lib.ERR_STATE                        # tensors missing
+    assert lib.nfai_decode(h, 0, None, None) == _lib.ERR_STATE                 # not finalized
+    assert lib.nfai_last_error(factory.ctx.handle)
+    assert lib.nfai_model_destroy(h) == _lib.OK
+
+
+def test_full_size_1b_properties(factory, oracle):
+    """The benchmark configuration at full size: determinism, prompt-vs-stepwise equality, a few oracle logits."""
+    cfg = synth.get_config("c1")
+    m = make(cfg, 160, factory)
+    toks = synth.prompt_ids(cfg, 128, 0)
+    logits, am = m.prefill(toks)
+    first, _ = m.decode_greedy(am, 16)
+    m.reset()
+    logits2, am2 = m.prefill(toks)
+    second, _ = m.decode_greedy(am2, 16)
+    assert np.array_equal(logits.view(np.uint32), logits2.view(np.uint32)) and am == am2
+    assert list(first) == list(second)
+    assert am == oracle.argmax(logits)
+    # oracle on the first 3 positions (about 2.5 GB of weights per CPU token)
+    ref = oracle.OracleModel(cfg, ctx=4).load_synthetic(0)
+    m.reset()
+    for t in toks[:3]:
+        want = ref.decode(int(t))
+        got, _ = m.decode(int(t))
+        assert float(np.abs(got - want).max()) <= ABS_F16
+    ms, nbytes = m.profile_kernel("ffn_gate_up", 8)
+    assert ms > 0 and nbytes == 2 * cfg.F * cfg.H * 2 + cfg.H * 4
+    assert m.step_launches() == 3 + 5 * cfg.L
+    m.Dispose()

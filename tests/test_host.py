@@ -1,0 +1,64 @@
+"""Host-side logic that needs no GPU: the synthetic generator, GGUF round trip, byte accounting."""
+import os
+
+import numpy as np
+
+from nfai_b200 import gguf_io, synth
+
+
+def test_tensor_streams_are_independent_and_seeded():
+    cfg = synth.get_config("c0")
+    a = synth.gen_tensor(cfg, "blk.1.attn_q.weight", (cfg.H, cfg.qDim), "f32", 0)
+    b = synth.gen_tensor(cfg, "blk.1.attn_q.weight", (cfg.H, cfg.qDim), "f32", 0)
+    c = synth.gen_tensor(cfg, "blk.0.attn_q.weight", (cfg.H, cfg.qDim), "f32", 0)
+    d = synth.gen_tensor(cfg, "blk.1.attn_q.weight", (cfg.H, cfg.qDim), "f32", 1)
+    assert np.array_equal(a, b) and not np.array_equal(a, c) and not np.array_equal(a, d)
+    assert a.shape == (cfg.qDim, cfg.H)
+    assert abs(float(a.std()) - 0.02) < 1e-3
+    g = synth.gen_tensor(cfg, "blk.0.attn_norm.weight", (cfg.H,), "f32", 0)
+    assert np.all(g == 1.0)
+
+
+def test_prompt_ids_are_in_range():
+    cfg = synth.get_config("c0")
+    p = synth.prompt_ids(cfg, 64, 0)
+    assert p.dtype == np.uint32 and p.shape == (64,) and p.max() < cfg.V
+    assert np.array_equal(p, synth.prompt_ids(cfg, 64, 0))
+
+
+def test_parameter_counts_match_the_architectures():
+    assert synth.get_config("c0").streamed_matrix_params() == 2_555_904
+    assert synth.get_config("c1").streamed_matrix_params() == 1_235_746_816
+    assert synth.get_config("c2").streamed_matrix_params() == 3_212_574_720
+    assert synth.get_config("c3").streamed_matrix_params() == 7_504_658_432
+
+
+def test_decode_bytes_formula():
+    cfg = synth.get_config("c1")
+    b0 = synth.decode_bytes(cfg, 0, 2)
+    b1 = synth.decode_bytes(cfg, 1, 2)
+    assert b1 - b0 == 2 * cfg.L * cfg.kvDim * 2  # one more position of K and V to read: 32 768 B
+    assert b1 - b0 == 32768
+    assert abs(synth.decode_bytes(cfg, 255, 2) - 2.480e9) < 0.01e9
+
+
+def test_gguf_round_trip(tmp_path):
+    cfg = synth.get_config("s3")
+    path = os.path.join(tmp_path, "s3.gguf")
+    gguf_io.write_synthetic_gguf(cfg, path, seed=3)
+    meta, tensors = gguf_io.read_gguf(path)
+    assert meta["general.architecture"] == "llama"
+    assert meta["llama.block_count"] == cfg.L
+    assert meta["llama.attention.head_count_kv"] == cfg.kvH
+    assert abs(meta["llama.rope.freq_base"] - 500000.0) < 1e-3
+    want = {n: (ne, dt, a) for n, ne, dt, a in synth.iter_tensors(cfg, 3)}
+    assert sorted(t.Name for t in tensors) == sorted(want)
+    for t in tensors:
+        ne, dt, a = want[t.Name]
+        assert tuple(t.Shape) == tuple(ne)
+        assert t.TypeSize == (2 if dt == "f16" else 4)
+        assert np.array_equal(t.to_numpy(), a)
+    # widened chunks are the float32 values of the halves, as the reference's GetDataRaw yields them
+    q = next(t for t in tensors if t.Name == "blk.0.attn_q.weight")
+    wide = np.frombuffer(b"".join(q.get_data_raw(widen_half=True)), np.float32)
+    assert np.array_equal(wide, want[q.Name][2].astype(np.float32).reshape(-1))
