@@ -179,6 +179,12 @@ int nfai_read_hidden(nfai_model* m, uint32_t layer, float* out);
  * avg_ms receives the mean duration of one launch; bytes_per_launch the algorithmic bytes it must move. */
 int nfai_profile_kernel(nfai_model* m, int which, int iters, float* avg_ms, uint64_t* bytes_per_launch);
 
+/* Launch shape of one GEMV kernel of the decode step (selector as in nfai_profile_kernel, 0..4): rows per warp
+ * (1, 2 or 4; the QKV and gate/up kernels need an even value), 16-byte loads in flight per row per lane
+ * (2, 4 or 8) and persistent CTAs per SM. Results do not depend on it. After nfai_model_finalize the decode
+ * graphs are captured again. No counterpart in the reference (its dispatch sizes are fixed in each shader class). */
+int nfai_model_tune(nfai_model* m, int which, int rows_per_warp, int unroll, int ctas_per_sm);
+
 /* Number of kernel launches inside one decode step (the captured graph's kernel nodes). */
 int nfai_step_launches(const nfai_model* m, int* out);
 

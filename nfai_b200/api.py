@@ -204,6 +204,10 @@ class LlamaModel:
               self.ctx.handle)
         return ms.value, nbytes.value
 
+    def tune(self, which: str, rows_per_warp: int, unroll: int, ctas_per_sm: int):
+        check(self._lib.nfai_model_tune(self.handle, self.KERNELS[which], rows_per_warp, unroll, ctas_per_sm),
+              self.ctx.handle)
+
     def step_launches(self) -> int:
         n = C.c_int()
         check(self._lib.nfai_step_launches(self.handle, C.byref(n)), self.ctx.handle)

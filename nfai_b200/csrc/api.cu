@@ -123,7 +123,7 @@ struct nfai_model {
   float* logits = nullptr;
   float* part_val = nullptr;
   uint32_t* part_idx = nullptr;
-  uint32_t nparts = 0;
+  uint32_t nparts = 0, nparts_alloc = 0;
   float* attn_part = nullptr;
   uint32_t* tickets = nullptr;
   uint32_t S_max = 1;
@@ -156,10 +156,12 @@ void read_tune(const char* name, GemvTune& t, int r_default, int u_default) {
   std::string key = std::string("NFAI_TUNE_") + name;
   const char* v = getenv(key.c_str());
   if (v) {
-    int r = 0, u = 0;
-    if (sscanf(v, "%d,%d", &r, &u) == 2 && (r == 1 || r == 2 || r == 4) && (u == 2 || u == 4 || u == 8)) {
+    int r = 0, u = 0, cps = 0;
+    int got = sscanf(v, "%d,%d,%d", &r, &u, &cps);
+    if (got >= 2 && (r == 1 || r == 2 || r == 4) && (u == 2 || u == 4 || u == 8)) {
       t.rows_per_warp = r;
       t.unroll = u;
+      if (got == 3 && cps >= 1 && cps <= 64) t.ctas_per_sm = cps;
     }
   }
 }
@@ -720,7 +722,9 @@ int nfai_model_finalize(nfai_model* m) {
   const size_t o_ao = take((size_t)m->qDimL * 4);
   const size_t o_h = take((size_t)m->Fl * 4);
   const size_t o_lg = take((size_t)m->Vl * 4);
-  const size_t npart_alloc = m->nparts > 8 ? m->nparts : 8;
+  // room for every launch shape nfai_model_tune may select later (up to 16 CTAs per SM)
+  const size_t npart_alloc = 148 * 16;
+  m->nparts_alloc = (uint32_t)npart_alloc;
   const size_t o_pv = take(npart_alloc * 4);
   const size_t o_pi = take(npart_alloc * 4);
   const size_t o_ap = take(attn_part_floats(m->qHl, hp.d, m->S_max) * 4);
@@ -934,6 +938,51 @@ int nfai_read_hidden(nfai_model* m, uint32_t layer, float* out) {
   if (layer >= m->hp.L || !out) return fail(c, NFAI_ERR_ARG, "layer out of range or null output");
   CU(c, cudaStreamSynchronize(c->stream));
   CU(c, cudaMemcpy(out, x_in(m, layer + 1), (size_t)m->hp.H * 4, cudaMemcpyDeviceToHost));
+  return NFAI_OK;
+}
+
+int nfai_model_tune(nfai_model* m, int which, int rows_per_warp, int unroll, int ctas_per_sm) {
+  if (!m) return fail(nullptr, NFAI_ERR_ARG, "model is null");
+  nfai_ctx* c = m->ctx;
+  GemvTune* t = which == 0 ? &m->tune_gateup : which == 1 ? &m->tune_down : which == 2 ? &m->tune_qkv
+              : which == 3 ? &m->tune_o : which == 4 ? &m->tune_head : nullptr;
+  if (!t) return fail(c, NFAI_ERR_ARG, "kernel selector must be 0..4");
+  const bool even_only = which == 0 || which == 2;
+  if (!(rows_per_warp == 1 || rows_per_warp == 2 || rows_per_warp == 4) || (even_only && rows_per_warp == 1) ||
+      !(unroll == 2 || unroll == 4 || unroll == 8) || rows_per_warp * unroll > 16 || ctas_per_sm < 1 || ctas_per_sm > 16)
+    return fail(c, NFAI_ERR_ARG, "unsupported launch shape");
+  GemvTune old = *t;
+  t->rows_per_warp = rows_per_warp;
+  t->unroll = unroll;
+  t->ctas_per_sm = ctas_per_sm;
+  if (!m->finalized) return NFAI_OK;
+  CU(c, cudaSetDevice(c->device));
+  CU(c, cudaStreamSynchronize(c->stream));
+  if (which == 4) {
+    GemvParams hp_ = head_params(m);
+    uint32_t np = gemv_grid(m->hp.weight_dtype, EPI_LOGITS, hp_, *t);
+    if (np > m->nparts_alloc) {
+      *t = old;
+      return fail(c, NFAI_ERR_ARG, "LM-head shape needs %u partials, %u were allocated", np, m->nparts_alloc);
+    }
+    m->nparts = np;
+  }
+  if (c->use_graph) {
+    cudaGraphExec_t gf = nullptr, gn = nullptr;
+    int launches = 0;
+    int rc = capture(m, true, false, &gf, &launches);
+    if (rc == NFAI_OK) rc = capture(m, false, true, &gn, nullptr);
+    if (rc != NFAI_OK) {
+      if (gf) cudaGraphExecDestroy(gf);
+      *t = old;
+      return rc;
+    }
+    cudaGraphExecDestroy(m->g_full);
+    cudaGraphExecDestroy(m->g_nohead);
+    m->g_full = gf;
+    m->g_nohead = gn;
+    m->launches_full = launches;
+  }
   return NFAI_OK;
 }
 

@@ -2,10 +2,12 @@
 // RoPE + KV-cache write, SiLU*up, logits + arg-max partials).
 //
 // The work is HBM-bound (one FMA per 2 or 4 weight bytes), so the kernel is a weight streamer:
-//  * a warp owns R consecutive rows; its lanes walk each row in 16-byte vectors (8 halves / 4 floats), 512
-//    contiguous bytes per warp per row per step;
-//  * U steps are issued back to back and the next batch is requested before the current one is consumed, so
-//    every lane keeps 2*U*R 16-byte loads in flight;
+//  * the grid is persistent: at most a few CTAs per SM, and every warp walks row blocks gw, gw + TW, gw + 2 TW ...
+//    (R consecutive rows each) as ONE continuous stream, so the prologue is paid once per CTA and the loads of
+//    the next row block are already in flight while the current one is reduced and stored;
+//  * the lanes walk a row in 16-byte vectors (8 halves / 4 floats), 512 contiguous bytes per warp per row per
+//    step; U steps are issued back to back and the next batch is requested before the current one is consumed,
+//    so every lane keeps 2*U*R 16-byte loads in flight;
 //  * the first batch is requested BEFORE the programmatic-dependency wait: the weights do not depend on the
 //    previous kernel, so they stream while it drains and while this CTA normalises x;
 //  * x (float32) sits in shared memory and is reused by all R rows of all warps; accumulation is float32;
@@ -24,8 +26,16 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
+constexpr uint32_t kNumSMs = 148;  // B200
 
 // ---- prologue: x (optionally RMS-normalised) into shared memory ----------------------------------------------
+// The gain is a weight: it can be staged in shared memory before the programmatic-dependency wait.
+__device__ __forceinline__ void load_gain(const GemvParams& p, float* xs) {
+  if (p.gain == nullptr) return;
+  float* gs = xs + p.K;
+  for (uint32_t i = threadIdx.x; i < p.K; i += kThreads) gs[i] = p.gain[i];
+}
+
 // ss = sum x^2 ; rms = sqrt(ss/K + eps) ; xs = (x / rms) * gain   (RMSNormShader.cs:136-148)
 __device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* red) {
   const uint32_t K = p.K;
@@ -35,6 +45,7 @@ __device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* re
     __syncthreads();
     return;
   }
+  const float* gs = xs + K;  // staged by load_gain() before the dependency wait
   float ss = 0.f;
   for (uint32_t i = tid; i < K; i += kThreads) {
     float v = p.x[i];
@@ -48,153 +59,164 @@ __device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* re
 #pragma unroll
   for (int w = 0; w < kWarps; ++w) tot += red[w];
   const float rms = sqrtf(__fdiv_rn(tot, (float)K) + p.eps);
-  for (uint32_t i = tid; i < K; i += kThreads) xs[i] = __fmul_rn(__fdiv_rn(xs[i], rms), p.gain[i]);
+  for (uint32_t i = tid; i < K; i += kThreads) xs[i] = __fmul_rn(__fdiv_rn(xs[i], rms), gs[i]);
   __syncthreads();
 }
 
-// ---- epilogues (lane 0 of the warp holds the R finished row sums) ---------------------------------------------
+// ---- epilogues (lane 0 of the warp holds the R finished row sums of one row block) --------------------------------
 template <typename KVT, int R, int EPI>
-__device__ __forceinline__ void epilogue(const GemvParams& p, uint32_t row0, const float (&acc)[R], float* red) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+__device__ __forceinline__ void row_epilogue(const GemvParams& p, uint32_t row0, const float (&acc)[R], float& best_v,
+                                             uint32_t& best_i) {
+  if ((threadIdx.x & 31) != 0) return;
   if constexpr (EPI == EPI_STORE) {
-    if (lane == 0) {
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        uint32_t n = row0 + r;
-        if (n < p.N) p.y[n] = p.resid ? p.resid[n] + acc[r] : acc[r];
-      }
+    for (int r = 0; r < R; ++r) {
+      uint32_t n = row0 + r;
+      if (n < p.N) p.y[n] = p.resid ? p.resid[n] + acc[r] : acc[r];
     }
   } else if constexpr (EPI == EPI_QKV_ROPE) {
     static_assert(R % 2 == 0, "RoPE pairs adjacent rows");
-    if (lane == 0) {
-      const uint32_t pos = p.state ? p.state->pos : p.pos_imm;
-      if (pos >= p.ctx) {
-        if (p.state) atomicOr(&p.state->err, 2u);
-        return;
-      }
+    const uint32_t pos = p.state ? p.state->pos : p.pos_imm;
+    if (pos >= p.ctx) {
+      if (p.state) atomicOr(&p.state->err, 2u);
+      return;
+    }
 #pragma unroll
-      for (int r = 0; r < R; r += 2) {
-        uint32_t n = row0 + r;
-        if (n >= p.N) break;
-        float a = acc[r], b = acc[r + 1];
-        if (n < p.qDim + p.kvDim) {  // Q or K: rotate the pair (2m, 2m+1) of its head
-          uint32_t local = n < p.qDim ? n : n - p.qDim;
-          uint32_t i = local % p.d;
-          if (i < p.ropeDim) {
-            float2 cs = p.rope_cs[(size_t)pos * (p.ropeDim / 2) + (i >> 1)];
-            // value1 = cos*a - sin*b ; value2 = sin*a + cos*b (RoPEShader.cs:256-257), products rounded separately
-            float v1 = __fsub_rn(__fmul_rn(cs.x, a), __fmul_rn(cs.y, b));
-            float v2 = __fadd_rn(__fmul_rn(cs.y, a), __fmul_rn(cs.x, b));
-            a = v1;
-            b = v2;
-          }
-          if (n < p.qDim) {
-            p.q_out[n] = a;
-            p.q_out[n + 1] = b;
-          } else {
-            KVT* kc = reinterpret_cast<KVT*>(p.kcache) + (size_t)pos * p.kvDim + local;
-            store_as(kc, a);
-            store_as(kc + 1, b);
-          }
-        } else {
-          KVT* vc = reinterpret_cast<KVT*>(p.vcache) + (size_t)pos * p.kvDim + (n - p.qDim - p.kvDim);
-          store_as(vc, a);
-          store_as(vc + 1, b);
+    for (int r = 0; r < R; r += 2) {
+      uint32_t n = row0 + r;
+      if (n >= p.N) break;
+      float a = acc[r], b = acc[r + 1];
+      if (n < p.qDim + p.kvDim) {  // Q or K: rotate the pair (2m, 2m+1) of its head
+        uint32_t local = n < p.qDim ? n : n - p.qDim;
+        uint32_t i = local % p.d;
+        if (i < p.ropeDim) {
+          float2 cs = p.rope_cs[(size_t)pos * (p.ropeDim / 2) + (i >> 1)];
+          // value1 = cos*a - sin*b ; value2 = sin*a + cos*b (RoPEShader.cs:256-257), products rounded separately
+          float v1 = __fsub_rn(__fmul_rn(cs.x, a), __fmul_rn(cs.y, b));
+          float v2 = __fadd_rn(__fmul_rn(cs.y, a), __fmul_rn(cs.x, b));
+          a = v1;
+          b = v2;
         }
+        if (n < p.qDim) {
+          p.q_out[n] = a;
+          p.q_out[n + 1] = b;
+        } else {
+          KVT* kc = reinterpret_cast<KVT*>(p.kcache) + (size_t)pos * p.kvDim + local;
+          store_as(kc, a);
+          store_as(kc + 1, b);
+        }
+      } else {
+        KVT* vc = reinterpret_cast<KVT*>(p.vcache) + (size_t)pos * p.kvDim + (n - p.qDim - p.kvDim);
+        store_as(vc, a);
+        store_as(vc + 1, b);
       }
     }
   } else if constexpr (EPI == EPI_SILU_MUL) {
     static_assert(R % 2 == 0, "gate and up rows are interleaved");
-    if (lane == 0) {
 #pragma unroll
-      for (int r = 0; r < R; r += 2) {
-        uint32_t n = row0 + r;
-        if (n >= p.N) break;
-        float gate = acc[r], up = acc[r + 1];
-        // sigmoid = 1/(1+exp(-x)); silu = x*sigmoid; h = up*silu (SiLUShader.cs:121-123, ElementWiseMul A=up,B=silu)
-        float sig = __fdiv_rn(1.0f, 1.0f + expf(-gate));
-        p.y[n >> 1] = __fmul_rn(up, __fmul_rn(gate, sig));
-      }
+    for (int r = 0; r < R; r += 2) {
+      uint32_t n = row0 + r;
+      if (n >= p.N) break;
+      float gate = acc[r], up = acc[r + 1];
+      // sigmoid = 1/(1+exp(-x)); silu = x*sigmoid; h = up*silu (SiLUShader.cs:121-123, ElementWiseMul A=up,B=silu)
+      float sig = __fdiv_rn(1.0f, 1.0f + expf(-gate));
+      p.y[n >> 1] = __fmul_rn(up, __fmul_rn(gate, sig));
     }
-  } else {  // EPI_LOGITS
-    float bv = -INFINITY;
-    uint32_t bi = 0xffffffffu;
-    if (lane == 0) {
+  } else {  // EPI_LOGITS: store and keep the warp's best (lowest index among equal maxima)
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        uint32_t n = row0 + r;
-        if (n < p.N) {
-          p.y[n] = acc[r];
-          if (bi == 0xffffffffu || acc[r] > bv) {
-            bv = acc[r];
-            bi = n;
-          }
+    for (int r = 0; r < R; ++r) {
+      uint32_t n = row0 + r;
+      if (n < p.N) {
+        p.y[n] = acc[r];
+        if (best_i == 0xffffffffu || acc[r] > best_v || (acc[r] == best_v && n < best_i)) {
+          best_v = acc[r];
+          best_i = n;
         }
       }
-      red[warp] = bv;
-      reinterpret_cast<uint32_t*>(red)[kWarps + warp] = bi;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float v = red[0];
-      uint32_t ix = reinterpret_cast<uint32_t*>(red)[kWarps];
-      for (int w = 1; w < kWarps; ++w) {
-        float wv = red[w];
-        uint32_t wi = reinterpret_cast<uint32_t*>(red)[kWarps + w];
-        if (wi != 0xffffffffu && (ix == 0xffffffffu || wv > v)) {  // ascending rows: strict > keeps the lowest index
-          v = wv;
-          ix = wi;
-        }
+  }
+}
+
+// EPI_LOGITS: one (max, lowest index) partial per CTA.
+__device__ __forceinline__ void cta_argmax_partial(const GemvParams& p, float best_v, uint32_t best_i, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t* redi = reinterpret_cast<uint32_t*>(red);
+  __syncthreads();  // red[] may still be read by the prologue of a slower warp
+  if (lane == 0) {
+    red[warp] = best_v;
+    redi[kWarps + warp] = best_i;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float v = red[0];
+    uint32_t ix = redi[kWarps];
+    for (int w = 1; w < kWarps; ++w) {
+      float wv = red[w];
+      uint32_t wi = redi[kWarps + w];
+      if (wi != 0xffffffffu && (ix == 0xffffffffu || wv > v || (wv == v && wi < ix))) {
+        v = wv;
+        ix = wi;
       }
-      p.part_val[blockIdx.x] = v;
-      p.part_idx[blockIdx.x] = ix;
     }
+    p.part_val[blockIdx.x] = v;
+    p.part_idx[blockIdx.x] = ix;
   }
 }
 
 // ---- the streamer ---------------------------------------------------------------------------------------------
 template <typename WT, typename KVT, int R, int U, int EPI>
-__global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(16) float smem[];
-  float* red = smem;       // 2*kWarps words of reduction scratch
-  float* xs = smem + 32;   // K floats
+  float* red = smem;      // 2*kWarps words of reduction scratch
+  float* xs = smem + 32;  // K floats of x, then K floats of gain
   constexpr int VE = WeightVec<WT>::kElems;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t row0 = (blockIdx.x * kWarps + warp) * R;
   const uint32_t nvec = p.K / VE;  // host guarantees K % VE == 0 and 16-byte aligned rows
-  const uint4* wrow[R];
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-    uint32_t n = row0 + r < p.N ? row0 + r : p.N - 1;  // clamp: tail warps re-read the last row, never out of bounds
-    wrow[r] = reinterpret_cast<const uint4*>(reinterpret_cast<const WT*>(p.W) + (size_t)n * p.K);
-  }
+  const uint32_t nkb = (nvec + 32 * U - 1) / (32 * U);  // batches per row block
+  const uint32_t nrb = (p.N + R - 1) / R;                // row blocks
+  const uint32_t TW = gridDim.x * kWarps;
+  const WT* const Wbase = reinterpret_cast<const WT*>(p.W);
   const uint4 zero = make_uint4(0, 0, 0, 0);
+
+  auto load_batch = [&](uint4(&buf)[U][R], uint32_t rb, uint32_t kb) {
+    if (rb >= nrb) return;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      uint32_t n = rb * R + r;
+      n = n < p.N ? n : p.N - 1;  // a ragged last block re-reads the last row, never out of bounds
+      const uint4* wrow = reinterpret_cast<const uint4*>(Wbase + (size_t)n * p.K);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        uint32_t v = kb * (32 * U) + lane + 32 * u;
+        buf[u][r] = v < nvec ? ld_stream16(wrow + v) : zero;
+      }
+    }
+  };
+
+  uint32_t rb = blockIdx.x * kWarps + warp, kb = 0;
   uint4 cur[U][R];
-#pragma unroll
-  for (int u = 0; u < U; ++u) {
-    uint32_t v = lane + 32 * u;
-#pragma unroll
-    for (int r = 0; r < R; ++r) cur[u][r] = v < nvec ? ld_stream16(wrow[r] + v) : zero;
-  }
+  load_batch(cur, rb, 0);  // weights do not depend on the previous kernel
+  load_gain(p, xs);
   pdl_launch_dependents();
   pdl_wait();
   load_x(p, xs, red);
 
+  float best_v = -INFINITY;
+  uint32_t best_i = 0xffffffffu;
   float acc[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) acc[r] = 0.f;
-  for (uint32_t base = 0; base < nvec; base += 32 * U) {
-    uint4 nxt[U][R];
-    const uint32_t nb = base + 32 * U;
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      uint32_t v = nb + lane + 32 * u;
-#pragma unroll
-      for (int r = 0; r < R; ++r) nxt[u][r] = v < nvec ? ld_stream16(wrow[r] + v) : zero;
+  while (rb < nrb) {
+    uint32_t nrb_next = rb, nkb_next = kb + 1;
+    if (nkb_next == nkb) {
+      nkb_next = 0;
+      nrb_next = rb + TW;
     }
+    uint4 nxt[U][R];
+    load_batch(nxt, nrb_next, nkb_next);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      uint32_t v = base + lane + 32 * u;
+      uint32_t v = kb * (32 * U) + lane + 32 * u;
       if (v < nvec) {
         float xv[VE];
         const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)v * VE);
@@ -215,14 +237,21 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
         }
       }
     }
+    if (nkb_next == 0) {  // the row block is complete
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r] = warp_sum(acc[r]);
+      row_epilogue<KVT, R, EPI>(p, rb * R, acc, best_v, best_i);
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r] = 0.f;
+    }
 #pragma unroll
     for (int u = 0; u < U; ++u)
 #pragma unroll
       for (int r = 0; r < R; ++r) cur[u][r] = nxt[u][r];
+    rb = nrb_next;
+    kb = nkb_next;
   }
-#pragma unroll
-  for (int r = 0; r < R; ++r) acc[r] = warp_sum(acc[r]);
-  epilogue<KVT, R, EPI>(p, row0, acc, red);
+  if constexpr (EPI == EPI_LOGITS) cta_argmax_partial(p, best_v, best_i, red);
 }
 
 // Same contract for any K and any alignment (element loads); used when K is not a multiple of the vector width.
@@ -233,20 +262,26 @@ __global__ void __launch_bounds__(kThreads) gemv_scalar_kernel(const GemvParams 
   float* xs = smem + 32;
   constexpr int R = 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t row0 = (blockIdx.x * kWarps + warp) * R;
+  const uint32_t nrb = (p.N + R - 1) / R;
+  load_gain(p, xs);
   pdl_launch_dependents();
   pdl_wait();
   load_x(p, xs, red);
-  float acc[R];
+  float best_v = -INFINITY;
+  uint32_t best_i = 0xffffffffu;
+  for (uint32_t rb = blockIdx.x * kWarps + warp; rb < nrb; rb += gridDim.x * kWarps) {
+    float acc[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    uint32_t n = row0 + r < p.N ? row0 + r : p.N - 1;
-    const WT* w = reinterpret_cast<const WT*>(p.W) + (size_t)n * p.K;
-    float a = 0.f;
-    for (uint32_t k = lane; k < p.K; k += 32) a = fmaf(to_float(w[k]), xs[k], a);
-    acc[r] = warp_sum(a);
+    for (int r = 0; r < R; ++r) {
+      uint32_t n = rb * R + r < p.N ? rb * R + r : p.N - 1;
+      const WT* w = reinterpret_cast<const WT*>(p.W) + (size_t)n * p.K;
+      float a = 0.f;
+      for (uint32_t k = lane; k < p.K; k += 32) a = fmaf(to_float(w[k]), xs[k], a);
+      acc[r] = warp_sum(a);
+    }
+    row_epilogue<KVT, R, EPI>(p, rb * R, acc, best_v, best_i);
   }
-  epilogue<KVT, R, EPI>(p, row0, acc, red);
+  if constexpr (EPI == EPI_LOGITS) cta_argmax_partial(p, best_v, best_i, red);
 }
 
 template <typename K>
@@ -327,7 +362,9 @@ int rows_per_warp(GemvEpilogue epi, bool vec, const GemvTune& t) {
 
 uint32_t gemv_grid(int wdtype, GemvEpilogue epi, const GemvParams& p, const GemvTune& t) {
   const uint32_t per_cta = kWarps * rows_per_warp(epi, vector_ok(wdtype, p), t);
-  return (p.N + per_cta - 1) / per_cta;
+  const uint32_t want = (p.N + per_cta - 1) / per_cta;
+  const uint32_t cap = kNumSMs * (uint32_t)(t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm);  // persistent: warps loop over row blocks
+  return want < cap ? want : cap;
 }
 
 cudaError_t launch_gemv(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue epi, const GemvParams& p,
@@ -337,7 +374,7 @@ cudaError_t launch_gemv(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue ep
   const bool vec = vector_ok(wdtype, p);
   const int R = rows_per_warp(epi, vec, t);
   dim3 grid(gemv_grid(wdtype, epi, p, t));
-  size_t smem = (32 + (size_t)p.K) * sizeof(float);
+  size_t smem = (32 + (size_t)p.K * (p.gain ? 2 : 1)) * sizeof(float);
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
   if (wdtype == 1) {
     if (kvdtype == 1) return launch_e<__half, __half>(epi, vec, R, t.unroll, grid, smem, s, pdl, p);

@@ -51,6 +51,7 @@ struct GemvParams {
 struct GemvTune {
   int rows_per_warp = 2;  // 1, 2 or 4 (EPI_QKV_ROPE and EPI_SILU_MUL need an even value)
   int unroll = 4;         // 16-byte loads in flight per row per lane: 2, 4 or 8
+  int ctas_per_sm = 2;    // persistent grid = min(needed, 148 * ctas_per_sm) CTAs of 256 threads
 };
 
 // Number of CTAs the launch will use (the LM head needs it to size its partial buffers).
@@ -71,7 +72,7 @@ struct AttnParams {
   uint32_t S_max = 1;
 };
 
-constexpr uint32_t kAttnTile = 32;       // positions per tile
+constexpr uint32_t kAttnMinChunk = 512;   // fewest positions one CTA takes before the range is split
 constexpr uint32_t kAttnHeadsPerCta = 4;  // query heads sharing one pass over K/V
 
 uint32_t attn_head_groups(uint32_t qH, uint32_t kvH);
