@@ -89,9 +89,10 @@ __global__ void __launch_bounds__(kAT, 1) attn_decode_kernel(const AttnParams p)
   constexpr int LPP = D / 8;    // lanes per position
   constexpr int PPW = 32 / LPP; // positions per warp step
   constexpr int UNR = KV8<KVT>::kUnroll;
-  constexpr int STR = D + 2;    // one partial: D accumulators, m, l
+  constexpr int STR = D + 2;    // one partial in scratch: D accumulators, m, l
+  constexpr int SSTR = D + 4;   // the same in shared memory, padded so that every row stays 16-byte aligned
 
-  __shared__ __align__(16) float wpart[kAW][kG][STR];  // per-warp partials
+  __shared__ __align__(16) float wpart[kAW][kG][SSTR];  // per-warp partials
   __shared__ float fin_scale[kAW][kG];
   __shared__ float fin_ML[kG][2];
   __shared__ uint32_t is_last;
