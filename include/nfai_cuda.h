@@ -179,11 +179,22 @@ int nfai_read_hidden(nfai_model* m, uint32_t layer, float* out);
  * avg_ms receives the mean duration of one launch; bytes_per_launch the algorithmic bytes it must move. */
 int nfai_profile_kernel(nfai_model* m, int which, int iters, float* avg_ms, uint64_t* bytes_per_launch);
 
-/* Launch shape of one GEMV kernel of the decode step (selector as in nfai_profile_kernel, 0..4): rows per warp
- * (1, 2 or 4; the QKV and gate/up kernels need an even value), 16-byte loads in flight per row per lane
- * (2, 4 or 8) and persistent CTAs per SM. Results do not depend on it. After nfai_model_finalize the decode
- * graphs are captured again. No counterpart in the reference (its dispatch sizes are fixed in each shader class). */
-int nfai_model_tune(nfai_model* m, int which, int rows_per_warp, int unroll, int ctas_per_sm);
+/* Launch shape of one GEMV kernel of the decode step (selector as in nfai_profile_kernel, 0..4).
+ * mode 0: weights double-buffered in registers; rows_per_warp in {1,2,4}, depth = 16-byte loads in flight per row
+ *         per lane in {2,4,8}.
+ * mode 1: weights staged through a shared-memory ring by bulk asynchronous copies; rows_per_warp in {1,2},
+ *         depth = ring stages per warp in {2,3,4,6}.
+ * The QKV and gate/up kernels need an even rows_per_warp. ctas_per_sm bounds the persistent grid. Results do not
+ * depend on the shape. After nfai_model_finalize the decode graphs are captured again.
+ * No counterpart in the reference (its dispatch sizes are fixed in each shader class). */
+int nfai_model_tune(nfai_model* m, int which, int mode, int rows_per_warp, int depth, int ctas_per_sm);
+
+/* L2 look-ahead of the decode step: every kernel asks the L2 for the step's weight sequence up to
+ * `lookahead_bytes` beyond the weights it consumes itself (`extra_bytes` further for kernels that read no
+ * weights), so that HBM keeps streaming across kernel boundaries and during attention. 0 switches it off.
+ * mode 0 = one prefetch per 128-byte line, 1 = bulk prefetches. Results do not depend on it.
+ * No counterpart in the reference. */
+int nfai_model_set_prefetch(nfai_model* m, uint64_t lookahead_bytes, uint64_t extra_bytes, int mode);
 
 /* Number of kernel launches inside one decode step (the captured graph's kernel nodes). */
 int nfai_step_launches(const nfai_model* m, int* out);

@@ -204,8 +204,12 @@ class LlamaModel:
               self.ctx.handle)
         return ms.value, nbytes.value
 
-    def tune(self, which: str, rows_per_warp: int, unroll: int, ctas_per_sm: int):
-        check(self._lib.nfai_model_tune(self.handle, self.KERNELS[which], rows_per_warp, unroll, ctas_per_sm),
+    def tune(self, which: str, mode: int, rows_per_warp: int, depth: int, ctas_per_sm: int):
+        check(self._lib.nfai_model_tune(self.handle, self.KERNELS[which], mode, rows_per_warp, depth, ctas_per_sm),
+              self.ctx.handle)
+
+    def set_prefetch(self, lookahead_bytes: int, extra_bytes: int = 0, mode: int = 1):
+        check(self._lib.nfai_model_set_prefetch(self.handle, int(lookahead_bytes), int(extra_bytes), mode),
               self.ctx.handle)
 
     def step_launches(self) -> int:

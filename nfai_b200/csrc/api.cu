@@ -136,6 +136,9 @@ struct nfai_model {
   int launches_full = 0;
   uint32_t pos = 0;  // host mirror of state->pos
   GemvTune tune_qkv, tune_o, tune_gateup, tune_down, tune_head;
+  // L2 look-ahead: how far beyond the weights a kernel consumes the step's weight sequence is requested
+  uint64_t pf_look = 0, pf_extra = 0;
+  int pf_mode = 1;
 };
 
 namespace {
@@ -156,12 +159,13 @@ void read_tune(const char* name, GemvTune& t, int r_default, int u_default) {
   std::string key = std::string("NFAI_TUNE_") + name;
   const char* v = getenv(key.c_str());
   if (v) {
-    int r = 0, u = 0, cps = 0;
-    int got = sscanf(v, "%d,%d,%d", &r, &u, &cps);
-    if (got >= 2 && (r == 1 || r == 2 || r == 4) && (u == 2 || u == 4 || u == 8)) {
+    int r = 0, u = 0, cps = 0, mode = 0;
+    int got = sscanf(v, "%d,%d,%d,%d", &r, &u, &cps, &mode);
+    if (got >= 2 && (r == 1 || r == 2 || r == 4) && (u == 2 || u == 3 || u == 4 || u == 6 || u == 8)) {
       t.rows_per_warp = r;
       t.unroll = u;
-      if (got == 3 && cps >= 1 && cps <= 64) t.ctas_per_sm = cps;
+      if (got >= 3 && cps >= 1 && cps <= 16) t.ctas_per_sm = cps;
+      if (got >= 4 && (mode == 0 || mode == 1)) t.mode = mode;
     }
   }
 }
@@ -264,6 +268,69 @@ GemvParams head_params(nfai_model* m) {
   return p;
 }
 
+// The weights of one step form a sequence in consumption order: the per-layer matrices (contiguous in the weight
+// arena, in the order the kernels read them) and then the LM-head matrix. Every kernel asks the L2 for the part
+// of that sequence between what earlier kernels already requested and `look` bytes beyond its own weights
+// (kernels without weights reach `extra` bytes further), wrapping into the next step at the end.
+struct PrefetchPlanner {
+  const char* baseA = nullptr;
+  uint64_t lenA = 0;
+  const char* baseB = nullptr;
+  uint64_t lenB = 0;
+  uint64_t look = 0, extra = 0, fetched = 0;
+  int mode = 1;
+  uint64_t total() const { return lenA + lenB; }
+  uint64_t off(const void* p) const { return (uint64_t)((const char*)p - baseA); }
+  PrefetchPlan next(uint64_t cons_end, bool has_weights) {
+    PrefetchPlan pl;
+    pl.mode = mode;
+    const uint64_t T = total();
+    if (look == 0 || T == 0) return pl;
+    uint64_t target = cons_end + look + (has_weights ? 0 : extra);
+    uint64_t a = fetched > cons_end ? fetched : cons_end, b = target;
+    if (target > fetched) fetched = target;
+    if (b <= a) return pl;
+    if (b - a > T) b = a + T;
+    int n = 0;
+    while (a < b && n < 2) {
+      uint64_t w = a % T;  // position inside one step's sequence
+      const bool inA = w < lenA;
+      uint64_t seg_end = inA ? lenA : T;
+      uint64_t len = b - a < seg_end - w ? b - a : seg_end - w;
+      const char* ptr = inA ? baseA + w : baseB + (w - lenA);
+      // whole 256-byte blocks: bulk prefetches need 16-byte multiples and the ranges are only hints
+      uint64_t lead = (256 - ((uintptr_t)ptr & 255)) & 255;
+      if (len > lead + 256) {
+        pl.ptr[n] = ptr + lead;
+        pl.bytes[n] = (len - lead) & ~255ull;
+        ++n;
+      }
+      a += len;
+    }
+    return pl;
+  }
+};
+
+PrefetchPlanner make_planner(nfai_model* m, bool with_head) {
+  PrefetchPlanner pp;
+  const LayerW& first = m->layers.front();
+  const LayerW& last = m->layers.back();
+  pp.baseA = (const char*)first.qkv.ptr;
+  pp.lenA = (uint64_t)((const char*)last.ffn_norm.ptr + (size_t)m->hp.H * 4 - pp.baseA);
+  if (with_head) {
+    GemvParams h = head_params(m);
+    pp.baseB = (const char*)h.W;
+    pp.lenB = (uint64_t)h.N * h.K * dtype_size(m->hp.weight_dtype);
+  }
+  pp.look = m->pf_look;
+  pp.extra = m->pf_extra;
+  pp.mode = m->pf_mode;
+  // what the tail of the previous step already requested
+  uint64_t carried = pp.look + pp.extra;
+  pp.fetched = carried < pp.total() ? carried : pp.total();
+  return pp;
+}
+
 cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* launches) {
   nfai_ctx* c = m->ctx;
   const nfai_hparams& hp = m->hp;
@@ -272,6 +339,8 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
   const int wdt = hp.weight_dtype, kvdt = hp.kv_dtype;
   int n = 0;
   cudaError_t e;
+  PrefetchPlanner pp = make_planner(m, with_head);
+  auto end_of = [&](const Matrix& M) { return pp.off(M.ptr) + M.bytes; };
 #define STEP(call)                 \
   do {                             \
     e = (call);                    \
@@ -279,30 +348,44 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     ++n;                           \
   } while (0)
   // the first kernel of a step must not overlap the previous step's tail: plain launch
-  STEP(launch_embed(s, wdt, m->embd.ptr, hp.H, hp.V, m->state, from_prompt ? m->prompt : nullptr, 0, x_in(m, 0), false));
+  STEP(launch_embed(s, wdt, m->embd.ptr, hp.H, hp.V, m->state, from_prompt ? m->prompt : nullptr, 0, x_in(m, 0),
+                    pp.next(0, false), false));
   for (uint32_t l = 0; l < hp.L; ++l) {
-    STEP(launch_gemv(s, wdt, kvdt, EPI_QKV_ROPE, qkv_params(m, l), m->tune_qkv, pdl));
-    STEP(launch_attn_decode(s, kvdt, attn_params(m, l), pdl));
-    STEP(launch_gemv(s, wdt, kvdt, EPI_STORE, o_params(m, l), m->tune_o, pdl));
+    const LayerW& LW = m->layers[l];
+    GemvParams gq = qkv_params(m, l);
+    gq.pf = pp.next(end_of(LW.qkv), true);
+    STEP(launch_gemv(s, wdt, kvdt, EPI_QKV_ROPE, gq, m->tune_qkv, pdl));
+    AttnParams ga = attn_params(m, l);
+    ga.pf = pp.next(end_of(LW.qkv), false);
+    STEP(launch_attn_decode(s, kvdt, ga, pdl));
+    GemvParams go = o_params(m, l);
+    go.pf = pp.next(end_of(LW.o), true);
+    STEP(launch_gemv(s, wdt, kvdt, EPI_STORE, go, m->tune_o, pdl));
     if (c->world > 1) {
       e = tp_allreduce_residual(c->tp, s, m->tp_buf, x_in(m, l), x_mid(m, l), hp.H, &n);
       if (e != cudaSuccess) return e;
     }
-    STEP(launch_gemv(s, wdt, kvdt, EPI_SILU_MUL, gateup_params(m, l), m->tune_gateup, pdl && c->world == 1));
-    STEP(launch_gemv(s, wdt, kvdt, EPI_STORE, down_params(m, l), m->tune_down, pdl));
+    GemvParams gg = gateup_params(m, l);
+    gg.pf = pp.next(end_of(LW.gateup), true);
+    STEP(launch_gemv(s, wdt, kvdt, EPI_SILU_MUL, gg, m->tune_gateup, pdl && c->world == 1));
+    GemvParams gd = down_params(m, l);
+    gd.pf = pp.next(pp.off(LW.ffn_norm.ptr) + (uint64_t)hp.H * 4, true);
+    STEP(launch_gemv(s, wdt, kvdt, EPI_STORE, gd, m->tune_down, pdl));
     if (c->world > 1) {
       e = tp_allreduce_residual(c->tp, s, m->tp_buf, x_mid(m, l), x_in(m, l + 1), hp.H, &n);
       if (e != cudaSuccess) return e;
     }
   }
   if (with_head) {
-    STEP(launch_gemv(s, wdt, kvdt, EPI_LOGITS, head_params(m), m->tune_head, pdl && c->world == 1));
+    GemvParams gh = head_params(m);
+    gh.pf = pp.next(pp.total(), true);
+    STEP(launch_gemv(s, wdt, kvdt, EPI_LOGITS, gh, m->tune_head, pdl && c->world == 1));
     if (c->world > 1) {
       e = tp_gather_argmax(c->tp, s, m->part_val, m->part_idx, m->nparts, m->v_lo, &n);
       if (e != cudaSuccess) return e;
     }
     STEP(launch_argmax_final(s, m->part_val, m->part_idx, c->world > 1 ? (uint32_t)c->world : m->nparts, m->state,
-                             nullptr, m->history, hp.ctx, pdl && c->world == 1));
+                             nullptr, m->history, hp.ctx, pp.next(pp.total(), false), pdl && c->world == 1));
   } else {
     STEP(launch_advance(s, m->state, pdl && c->world == 1));
   }
@@ -623,10 +706,13 @@ int nfai_model_create(nfai_ctx* c, const nfai_hparams* hp, nfai_model** out) {
     fix(L.qkv.ptr); fix(L.o.ptr); fix(L.gateup.ptr); fix(L.down.ptr);
     fixg(L.attn_norm); fixg(L.ffn_norm);
   }
+  m->pf_look = (uint64_t)env_int("NFAI_PF_MB", 0) << 20;
+  m->pf_extra = (uint64_t)env_int("NFAI_PF_EXTRA_MB", 0) << 20;
+  m->pf_mode = env_int("NFAI_PF_MODE", 1);
   read_tune("QKV", m->tune_qkv, 2, 4);
-  read_tune("O", m->tune_o, 1, 4);
+  read_tune("O", m->tune_o, 2, 4);
   read_tune("GATEUP", m->tune_gateup, 2, 4);
-  read_tune("DOWN", m->tune_down, 1, 4);
+  read_tune("DOWN", m->tune_down, 2, 4);
   read_tune("HEAD", m->tune_head, 2, 4);
   *out = m;
   return NFAI_OK;
@@ -941,19 +1027,24 @@ int nfai_read_hidden(nfai_model* m, uint32_t layer, float* out) {
   return NFAI_OK;
 }
 
-int nfai_model_tune(nfai_model* m, int which, int rows_per_warp, int unroll, int ctas_per_sm) {
+int nfai_model_tune(nfai_model* m, int which, int mode, int rows_per_warp, int depth, int ctas_per_sm) {
   if (!m) return fail(nullptr, NFAI_ERR_ARG, "model is null");
   nfai_ctx* c = m->ctx;
   GemvTune* t = which == 0 ? &m->tune_gateup : which == 1 ? &m->tune_down : which == 2 ? &m->tune_qkv
               : which == 3 ? &m->tune_o : which == 4 ? &m->tune_head : nullptr;
   if (!t) return fail(c, NFAI_ERR_ARG, "kernel selector must be 0..4");
   const bool even_only = which == 0 || which == 2;
-  if (!(rows_per_warp == 1 || rows_per_warp == 2 || rows_per_warp == 4) || (even_only && rows_per_warp == 1) ||
-      !(unroll == 2 || unroll == 4 || unroll == 8) || rows_per_warp * unroll > 16 || ctas_per_sm < 1 || ctas_per_sm > 16)
-    return fail(c, NFAI_ERR_ARG, "unsupported launch shape");
+  bool ok = (mode == 0 || mode == 1) && ctas_per_sm >= 1 && ctas_per_sm <= 16 && !(even_only && rows_per_warp == 1);
+  if (mode == 0)
+    ok = ok && (rows_per_warp == 1 || rows_per_warp == 2 || rows_per_warp == 4) && (depth == 2 || depth == 4 || depth == 8) &&
+         rows_per_warp * depth <= 16;
+  else
+    ok = ok && (rows_per_warp == 1 || rows_per_warp == 2) && (depth == 2 || depth == 3 || depth == 4 || depth == 6);
+  if (!ok) return fail(c, NFAI_ERR_ARG, "unsupported launch shape");
   GemvTune old = *t;
+  t->mode = mode;
   t->rows_per_warp = rows_per_warp;
-  t->unroll = unroll;
+  t->unroll = depth;
   t->ctas_per_sm = ctas_per_sm;
   if (!m->finalized) return NFAI_OK;
   CU(c, cudaSetDevice(c->device));
@@ -983,6 +1074,32 @@ int nfai_model_tune(nfai_model* m, int which, int rows_per_warp, int unroll, int
     m->g_nohead = gn;
     m->launches_full = launches;
   }
+  return NFAI_OK;
+}
+
+int nfai_model_set_prefetch(nfai_model* m, uint64_t lookahead_bytes, uint64_t extra_bytes, int mode) {
+  if (!m) return fail(nullptr, NFAI_ERR_ARG, "model is null");
+  nfai_ctx* c = m->ctx;
+  if (mode != 0 && mode != 1) return fail(c, NFAI_ERR_ARG, "mode must be 0 (per line) or 1 (bulk)");
+  m->pf_look = lookahead_bytes;
+  m->pf_extra = extra_bytes;
+  m->pf_mode = mode;
+  if (!m->finalized || !c->use_graph) return NFAI_OK;
+  CU(c, cudaSetDevice(c->device));
+  CU(c, cudaStreamSynchronize(c->stream));
+  cudaGraphExec_t gf = nullptr, gn = nullptr;
+  int launches = 0;
+  int rc = capture(m, true, false, &gf, &launches);
+  if (rc == NFAI_OK) rc = capture(m, false, true, &gn, nullptr);
+  if (rc != NFAI_OK) {
+    if (gf) cudaGraphExecDestroy(gf);
+    return rc;
+  }
+  cudaGraphExecDestroy(m->g_full);
+  cudaGraphExecDestroy(m->g_nohead);
+  m->g_full = gf;
+  m->g_nohead = gn;
+  m->launches_full = launches;
   return NFAI_OK;
 }
 
@@ -1019,10 +1136,29 @@ int nfai_profile_kernel(nfai_model* m, int which, int iters, float* avg_ms, uint
       default: return launch_attn_decode(c->stream, kvdt, attn_params(m, l), false);
     }
   };
-  for (int i = 0; i < 3; ++i) CU(c, one(i));
-  CU(c, cudaEventRecord(c->ev0, c->stream));
-  for (int i = 0; i < iters; ++i) CU(c, one(i));
-  CU(c, cudaEventRecord(c->ev1, c->stream));
+  // the launches are captured into a graph so that short kernels are timed on the device, not at the rate the
+  // host can issue them
+  cudaGraph_t g = nullptr;
+  cudaGraphExec_t ge = nullptr;
+  CU(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+  cudaError_t le = cudaSuccess;
+  for (int i = 0; i < iters && le == cudaSuccess; ++i) le = one(i);
+  cudaError_t ee = cudaStreamEndCapture(c->stream, &g);
+  if (le != cudaSuccess || ee != cudaSuccess) {
+    if (g) cudaGraphDestroy(g);
+    cudaGetLastError();
+    return fail(c, NFAI_ERR_CUDA, "profile capture failed: %s / %s", cudaGetErrorString(le), cudaGetErrorString(ee));
+  }
+  le = cudaGraphInstantiate(&ge, g, 0);
+  cudaGraphDestroy(g);
+  if (le != cudaSuccess) return fail(c, NFAI_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(le));
+  le = cudaGraphLaunch(ge, c->stream);  // warm-up
+  if (le == cudaSuccess) le = cudaEventRecord(c->ev0, c->stream);
+  if (le == cudaSuccess) le = cudaGraphLaunch(ge, c->stream);
+  if (le == cudaSuccess) le = cudaEventRecord(c->ev1, c->stream);
+  if (le == cudaSuccess) le = cudaStreamSynchronize(c->stream);
+  cudaGraphExecDestroy(ge);
+  if (le != cudaSuccess) return fail(c, NFAI_ERR_CUDA, "profile run failed: %s", cudaGetErrorString(le));
   if ((rc = set_state_word(m, offsetof(StepState, pos), saved_pos, 4))) return rc;
   CU(c, cudaStreamSynchronize(c->stream));
   float ms = 0.f;
@@ -1065,7 +1201,7 @@ int nfai_op_embed(nfai_ctx* c, const void* E, int dtype, uint32_t H, uint32_t V,
   if (rc) return rc;
   if (!E || !x_out || bad_dtype(dtype) || !H) return fail(c, NFAI_ERR_ARG, "bad argument");
   if (token >= V) return fail(c, NFAI_ERR_ARG, "token id %u out of range (V = %u)", token, V);
-  return op_end(c, launch_embed(c->stream, dtype, E, H, V, nullptr, nullptr, token, x_out, false));
+  return op_end(c, launch_embed(c->stream, dtype, E, H, V, nullptr, nullptr, token, x_out, PrefetchPlan(), false));
 }
 
 int nfai_op_gemv(nfai_ctx* c, const void* W, int dtype, uint32_t N, uint32_t K, const float* x, const float* gain, float eps,
@@ -1151,7 +1287,7 @@ int nfai_op_lm_head(nfai_ctx* c, const void* W, int dtype, const float* x, const
   p.part_val = pv;
   p.part_idx = (uint32_t*)(pv + nparts);
   cudaError_t e = launch_gemv(c->stream, dtype, NFAI_F32, EPI_LOGITS, p, t, false);
-  if (e == cudaSuccess) e = launch_argmax_final(c->stream, p.part_val, p.part_idx, nparts, nullptr, argmax_out, nullptr, 0, false);
+  if (e == cudaSuccess) e = launch_argmax_final(c->stream, p.part_val, p.part_idx, nparts, nullptr, argmax_out, nullptr, 0, PrefetchPlan(), false);
   cudaFreeAsync(pv, c->stream);
   return op_end(c, e);
 }

@@ -97,6 +97,7 @@ __global__ void __launch_bounds__(kAT, 1) attn_decode_kernel(const AttnParams p)
   __shared__ float fin_ML[kG][2];
   __shared__ uint32_t is_last;
 
+  prefetch_plan(p.pf, kPrefetchChunk);
   pdl_launch_dependents();
   pdl_wait();  // q, K and V of this position come from the previous kernel
 

@@ -36,6 +36,35 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Ask the L2 for [ptr, ptr+bytes) of both ranges of a plan, the work split over every thread of the grid.
+// Nothing waits for the data: it is a hint that keeps HBM busy for the kernels that follow.
+template <typename Plan>
+__device__ __forceinline__ void prefetch_plan(const Plan& pf, uint32_t chunk) {
+  const unsigned long long nthreads = (unsigned long long)gridDim.x * gridDim.y * blockDim.x;
+  const unsigned long long gtid =
+      ((unsigned long long)blockIdx.y * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const char* base = pf.ptr[r];
+    const unsigned long long bytes = pf.bytes[r];
+    if (bytes == 0) continue;
+    if (pf.mode == 0) {
+      for (unsigned long long off = gtid * 128ull; off < bytes; off += nthreads * 128ull)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
+    } else {
+      // one lane per warp issues bulk prefetches; sizes are multiples of 16 bytes (the plan is 256-byte aligned)
+      if ((threadIdx.x & 31) == 0) {
+        const unsigned long long nwarps = nthreads >> 5, gw = gtid >> 5;
+        for (unsigned long long off = gw * chunk; off < bytes; off += nwarps * chunk) {
+          unsigned long long n = bytes - off < chunk ? bytes - off : chunk;
+          n &= ~15ull;
+          if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"((uint32_t)n) : "memory");
+        }
+      }
+    }
+  }
+}
+
 // Unpack a 16-byte vector of weights into float32 (exact widening).
 template <typename WT>
 struct WeightVec;

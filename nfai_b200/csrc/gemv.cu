@@ -17,151 +17,13 @@
 // Reference arithmetic this replaces: NFAI.Vulkan.Shaders/MatrixMultiplyShader.cs:266-288 (one thread per
 // output, serial k loop), RMSNormShader.cs:129-150, RoPEShader.cs:238-271, SiLUShader.cs:112-127,
 // ElementWiseMultiplicationShader.cs:127-138, host residual adds at TransformerBlock.cs:151-161,174-181.
-#include "common.cuh"
-#include "kernels.h"
+#include "gemv_common.cuh"
 
 namespace nfai {
 
+using namespace gemv_detail;
+
 namespace {
-
-constexpr int kThreads = 256;
-constexpr int kWarps = kThreads / 32;
-constexpr uint32_t kNumSMs = 148;  // B200
-
-// ---- prologue: x (optionally RMS-normalised) into shared memory ----------------------------------------------
-// The gain is a weight: it can be staged in shared memory before the programmatic-dependency wait.
-__device__ __forceinline__ void load_gain(const GemvParams& p, float* xs) {
-  if (p.gain == nullptr) return;
-  float* gs = xs + p.K;
-  for (uint32_t i = threadIdx.x; i < p.K; i += kThreads) gs[i] = p.gain[i];
-}
-
-// ss = sum x^2 ; rms = sqrt(ss/K + eps) ; xs = (x / rms) * gain   (RMSNormShader.cs:136-148)
-__device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* red) {
-  const uint32_t K = p.K;
-  const int tid = threadIdx.x;
-  if (p.gain == nullptr) {
-    for (uint32_t i = tid; i < K; i += kThreads) xs[i] = p.x[i];
-    __syncthreads();
-    return;
-  }
-  const float* gs = xs + K;  // staged by load_gain() before the dependency wait
-  float ss = 0.f;
-  for (uint32_t i = tid; i < K; i += kThreads) {
-    float v = p.x[i];
-    xs[i] = v;
-    ss = fmaf(v, v, ss);
-  }
-  ss = warp_sum(ss);
-  if ((tid & 31) == 0) red[tid >> 5] = ss;
-  __syncthreads();
-  float tot = 0.f;
-#pragma unroll
-  for (int w = 0; w < kWarps; ++w) tot += red[w];
-  const float rms = sqrtf(__fdiv_rn(tot, (float)K) + p.eps);
-  for (uint32_t i = tid; i < K; i += kThreads) xs[i] = __fmul_rn(__fdiv_rn(xs[i], rms), gs[i]);
-  __syncthreads();
-}
-
-// ---- epilogues (lane 0 of the warp holds the R finished row sums of one row block) --------------------------------
-template <typename KVT, int R, int EPI>
-__device__ __forceinline__ void row_epilogue(const GemvParams& p, uint32_t row0, const float (&acc)[R], float& best_v,
-                                             uint32_t& best_i) {
-  if ((threadIdx.x & 31) != 0) return;
-  if constexpr (EPI == EPI_STORE) {
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      uint32_t n = row0 + r;
-      if (n < p.N) p.y[n] = p.resid ? p.resid[n] + acc[r] : acc[r];
-    }
-  } else if constexpr (EPI == EPI_QKV_ROPE) {
-    static_assert(R % 2 == 0, "RoPE pairs adjacent rows");
-    const uint32_t pos = p.state ? p.state->pos : p.pos_imm;
-    if (pos >= p.ctx) {
-      if (p.state) atomicOr(&p.state->err, 2u);
-      return;
-    }
-#pragma unroll
-    for (int r = 0; r < R; r += 2) {
-      uint32_t n = row0 + r;
-      if (n >= p.N) break;
-      float a = acc[r], b = acc[r + 1];
-      if (n < p.qDim + p.kvDim) {  // Q or K: rotate the pair (2m, 2m+1) of its head
-        uint32_t local = n < p.qDim ? n : n - p.qDim;
-        uint32_t i = local % p.d;
-        if (i < p.ropeDim) {
-          float2 cs = p.rope_cs[(size_t)pos * (p.ropeDim / 2) + (i >> 1)];
-          // value1 = cos*a - sin*b ; value2 = sin*a + cos*b (RoPEShader.cs:256-257), products rounded separately
-          float v1 = __fsub_rn(__fmul_rn(cs.x, a), __fmul_rn(cs.y, b));
-          float v2 = __fadd_rn(__fmul_rn(cs.y, a), __fmul_rn(cs.x, b));
-          a = v1;
-          b = v2;
-        }
-        if (n < p.qDim) {
-          p.q_out[n] = a;
-          p.q_out[n + 1] = b;
-        } else {
-          KVT* kc = reinterpret_cast<KVT*>(p.kcache) + (size_t)pos * p.kvDim + local;
-          store_as(kc, a);
-          store_as(kc + 1, b);
-        }
-      } else {
-        KVT* vc = reinterpret_cast<KVT*>(p.vcache) + (size_t)pos * p.kvDim + (n - p.qDim - p.kvDim);
-        store_as(vc, a);
-        store_as(vc + 1, b);
-      }
-    }
-  } else if constexpr (EPI == EPI_SILU_MUL) {
-    static_assert(R % 2 == 0, "gate and up rows are interleaved");
-#pragma unroll
-    for (int r = 0; r < R; r += 2) {
-      uint32_t n = row0 + r;
-      if (n >= p.N) break;
-      float gate = acc[r], up = acc[r + 1];
-      // sigmoid = 1/(1+exp(-x)); silu = x*sigmoid; h = up*silu (SiLUShader.cs:121-123, ElementWiseMul A=up,B=silu)
-      float sig = __fdiv_rn(1.0f, 1.0f + expf(-gate));
-      p.y[n >> 1] = __fmul_rn(up, __fmul_rn(gate, sig));
-    }
-  } else {  // EPI_LOGITS: store and keep the warp's best (lowest index among equal maxima)
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      uint32_t n = row0 + r;
-      if (n < p.N) {
-        p.y[n] = acc[r];
-        if (best_i == 0xffffffffu || acc[r] > best_v || (acc[r] == best_v && n < best_i)) {
-          best_v = acc[r];
-          best_i = n;
-        }
-      }
-    }
-  }
-}
-
-// EPI_LOGITS: one (max, lowest index) partial per CTA.
-__device__ __forceinline__ void cta_argmax_partial(const GemvParams& p, float best_v, uint32_t best_i, float* red) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint32_t* redi = reinterpret_cast<uint32_t*>(red);
-  __syncthreads();  // red[] may still be read by the prologue of a slower warp
-  if (lane == 0) {
-    red[warp] = best_v;
-    redi[kWarps + warp] = best_i;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float v = red[0];
-    uint32_t ix = redi[kWarps];
-    for (int w = 1; w < kWarps; ++w) {
-      float wv = red[w];
-      uint32_t wi = redi[kWarps + w];
-      if (wi != 0xffffffffu && (ix == 0xffffffffu || wv > v || (wv == v && wi < ix))) {
-        v = wv;
-        ix = wi;
-      }
-    }
-    p.part_val[blockIdx.x] = v;
-    p.part_idx[blockIdx.x] = ix;
-  }
-}
 
 // ---- the streamer ---------------------------------------------------------------------------------------------
 template <typename WT, typename KVT, int R, int U, int EPI>
@@ -197,6 +59,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
   uint4 cur[U][R];
   load_batch(cur, rb, 0);  // weights do not depend on the previous kernel
   load_gain(p, xs);
+  prefetch_plan(p.pf, kPrefetchChunk);
   pdl_launch_dependents();
   pdl_wait();
   load_x(p, xs, red);
@@ -264,6 +127,7 @@ __global__ void __launch_bounds__(kThreads) gemv_scalar_kernel(const GemvParams 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t nrb = (p.N + R - 1) / R;
   load_gain(p, xs);
+  prefetch_plan(p.pf, kPrefetchChunk);
   pdl_launch_dependents();
   pdl_wait();
   load_x(p, xs, red);
@@ -286,8 +150,9 @@ __global__ void __launch_bounds__(kThreads) gemv_scalar_kernel(const GemvParams 
 
 template <typename K>
 cudaError_t launch_k(K kernel, dim3 grid, size_t smem, cudaStream_t s, bool pdl, const GemvParams& p) {
+  cudaError_t e = cudaSuccess;
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
   cudaLaunchConfig_t cfg = {};
@@ -360,7 +225,18 @@ int rows_per_warp(GemvEpilogue epi, bool vec, const GemvTune& t) {
 
 }  // namespace
 
+static bool use_ring(int wdtype, GemvEpilogue epi, const GemvParams& p, const GemvTune& t, int* R) {
+  if (t.mode != 1 || !vector_ok(wdtype, p)) return false;
+  int r = t.rows_per_warp >= 2 ? 2 : 1;
+  if (epi == EPI_QKV_ROPE || epi == EPI_SILU_MUL) r = 2;
+  if (gemv_ring_smem(p, r, t.unroll) > 227 * 1024) return false;
+  *R = r;
+  return true;
+}
+
 uint32_t gemv_grid(int wdtype, GemvEpilogue epi, const GemvParams& p, const GemvTune& t) {
+  int ring_R = 0;
+  if (use_ring(wdtype, epi, p, t, &ring_R)) return gemv_ring_grid(p, ring_R, t.ctas_per_sm);
   const uint32_t per_cta = kWarps * rows_per_warp(epi, vector_ok(wdtype, p), t);
   const uint32_t want = (p.N + per_cta - 1) / per_cta;
   const uint32_t cap = kNumSMs * (uint32_t)(t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm);  // persistent: warps loop over row blocks
@@ -371,6 +247,9 @@ cudaError_t launch_gemv(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue ep
                         const GemvTune& t, bool pdl) {
   if (p.N == 0 || p.K == 0) return cudaErrorInvalidValue;
   if ((epi == EPI_QKV_ROPE || epi == EPI_SILU_MUL) && (p.N % 2) != 0) return cudaErrorInvalidValue;
+  int ring_R = 0;
+  if (use_ring(wdtype, epi, p, t, &ring_R))
+    return launch_gemv_ring(s, wdtype, kvdtype, epi, p, ring_R, t.unroll, t.ctas_per_sm, pdl);
   const bool vec = vector_ok(wdtype, p);
   const int R = rows_per_warp(epi, vec, t);
   dim3 grid(gemv_grid(wdtype, epi, p, t));

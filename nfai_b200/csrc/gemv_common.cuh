@@ -1,0 +1,149 @@
+// Prologue (x, optional RMSNorm) and epilogues shared by the GEMV kernels of the decode step.
+#pragma once
+#include "common.cuh"
+#include "kernels.h"
+
+namespace nfai {
+namespace gemv_detail {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr uint32_t kNumSMs = 148;  // B200
+
+// ---- prologue: x (optionally RMS-normalised) into shared memory ----------------------------------------------
+// The gain is a weight: it can be staged in shared memory before the programmatic-dependency wait.
+__device__ __forceinline__ void load_gain(const GemvParams& p, float* xs) {
+  if (p.gain == nullptr) return;
+  float* gs = xs + p.K;
+  for (uint32_t i = threadIdx.x; i < p.K; i += kThreads) gs[i] = p.gain[i];
+}
+
+// ss = sum x^2 ; rms = sqrt(ss/K + eps) ; xs = (x / rms) * gain   (RMSNormShader.cs:136-148)
+__device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* red) {
+  const uint32_t K = p.K;
+  const int tid = threadIdx.x;
+  if (p.gain == nullptr) {
+    for (uint32_t i = tid; i < K; i += kThreads) xs[i] = p.x[i];
+    __syncthreads();
+    return;
+  }
+  const float* gs = xs + K;  // staged by load_gain() before the dependency wait
+  float ss = 0.f;
+  for (uint32_t i = tid; i < K; i += kThreads) {
+    float v = p.x[i];
+    xs[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) tot += red[w];
+  const float rms = sqrtf(__fdiv_rn(tot, (float)K) + p.eps);
+  for (uint32_t i = tid; i < K; i += kThreads) xs[i] = __fmul_rn(__fdiv_rn(xs[i], rms), gs[i]);
+  __syncthreads();
+}
+
+// ---- epilogues (lane 0 of the warp holds the R finished row sums of one row block) --------------------------------
+template <typename KVT, int R, int EPI>
+__device__ __forceinline__ void row_epilogue(const GemvParams& p, uint32_t row0, const float (&acc)[R], float& best_v,
+                                             uint32_t& best_i) {
+  if ((threadIdx.x & 31) != 0) return;
+  if constexpr (EPI == EPI_STORE) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      uint32_t n = row0 + r;
+      if (n < p.N) p.y[n] = p.resid ? p.resid[n] + acc[r] : acc[r];
+    }
+  } else if constexpr (EPI == EPI_QKV_ROPE) {
+    static_assert(R % 2 == 0, "RoPE pairs adjacent rows");
+    const uint32_t pos = p.state ? p.state->pos : p.pos_imm;
+    if (pos >= p.ctx) {
+      if (p.state) atomicOr(&p.state->err, 2u);
+      return;
+    }
+#pragma unroll
+    for (int r = 0; r < R; r += 2) {
+      uint32_t n = row0 + r;
+      if (n >= p.N) break;
+      float a = acc[r], b = acc[r + 1];
+      if (n < p.qDim + p.kvDim) {  // Q or K: rotate the pair (2m, 2m+1) of its head
+        uint32_t local = n < p.qDim ? n : n - p.qDim;
+        uint32_t i = local % p.d;
+        if (i < p.ropeDim) {
+          float2 cs = p.rope_cs[(size_t)pos * (p.ropeDim / 2) + (i >> 1)];
+          // value1 = cos*a - sin*b ; value2 = sin*a + cos*b (RoPEShader.cs:256-257), products rounded separately
+          float v1 = __fsub_rn(__fmul_rn(cs.x, a), __fmul_rn(cs.y, b));
+          float v2 = __fadd_rn(__fmul_rn(cs.y, a), __fmul_rn(cs.x, b));
+          a = v1;
+          b = v2;
+        }
+        if (n < p.qDim) {
+          p.q_out[n] = a;
+          p.q_out[n + 1] = b;
+        } else {
+          KVT* kc = reinterpret_cast<KVT*>(p.kcache) + (size_t)pos * p.kvDim + local;
+          store_as(kc, a);
+          store_as(kc + 1, b);
+        }
+      } else {
+        KVT* vc = reinterpret_cast<KVT*>(p.vcache) + (size_t)pos * p.kvDim + (n - p.qDim - p.kvDim);
+        store_as(vc, a);
+        store_as(vc + 1, b);
+      }
+    }
+  } else if constexpr (EPI == EPI_SILU_MUL) {
+    static_assert(R % 2 == 0, "gate and up rows are interleaved");
+#pragma unroll
+    for (int r = 0; r < R; r += 2) {
+      uint32_t n = row0 + r;
+      if (n >= p.N) break;
+      float gate = acc[r], up = acc[r + 1];
+      // sigmoid = 1/(1+exp(-x)); silu = x*sigmoid; h = up*silu (SiLUShader.cs:121-123, ElementWiseMul A=up,B=silu)
+      float sig = __fdiv_rn(1.0f, 1.0f + expf(-gate));
+      p.y[n >> 1] = __fmul_rn(up, __fmul_rn(gate, sig));
+    }
+  } else {  // EPI_LOGITS: store and keep the warp's best (lowest index among equal maxima)
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      uint32_t n = row0 + r;
+      if (n < p.N) {
+        p.y[n] = acc[r];
+        if (best_i == 0xffffffffu || acc[r] > best_v || (acc[r] == best_v && n < best_i)) {
+          best_v = acc[r];
+          best_i = n;
+        }
+      }
+    }
+  }
+}
+
+// EPI_LOGITS: one (max, lowest index) partial per CTA.
+__device__ __forceinline__ void cta_argmax_partial(const GemvParams& p, float best_v, uint32_t best_i, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t* redi = reinterpret_cast<uint32_t*>(red);
+  __syncthreads();  // red[] may still be read by the prologue of a slower warp
+  if (lane == 0) {
+    red[warp] = best_v;
+    redi[kWarps + warp] = best_i;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float v = red[0];
+    uint32_t ix = redi[kWarps];
+    for (int w = 1; w < kWarps; ++w) {
+      float wv = red[w];
+      uint32_t wi = redi[kWarps + w];
+      if (wi != 0xffffffffu && (ix == 0xffffffffu || wv > v || (wv == v && wi < ix))) {
+        v = wv;
+        ix = wi;
+      }
+    }
+    p.part_val[blockIdx.x] = v;
+    p.part_idx[blockIdx.x] = ix;
+  }
+}
+
+}  // namespace gemv_detail
+}  // namespace nfai

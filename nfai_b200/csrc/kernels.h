@@ -6,6 +6,14 @@
 
 namespace nfai {
 
+// Kernels that stage their stream in shared memory ask for the largest shared-memory carve-out. Kernels that
+// stream through registers must NOT: loads in flight occupy L1 lines, so shrinking the L1 cuts their bandwidth
+// (measured: the register streamer lost 20% with the maximum carve-out).
+template <typename Kern>
+inline cudaError_t prefer_max_shared(Kern kernel) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+}
+
 // Device-resident state of one model: the graph's kernels read and advance it so that one captured graph
 // serves every position.
 struct StepState {
@@ -17,6 +25,16 @@ struct StepState {
   uint32_t steps;       // number of steps executed (diagnostics)
   uint32_t pad[2];
 };
+
+// Weights a kernel asks the L2 to fetch for the kernels that follow it (up to two address ranges): HBM keeps
+// streaming the weight sequence of the step while a kernel is waiting on its predecessor, normalising x or
+// running attention. mode 0 = one prefetch per 128-byte line, 1 = bulk prefetches of kPrefetchChunk bytes.
+struct PrefetchPlan {
+  const char* ptr[2] = {nullptr, nullptr};
+  unsigned long long bytes[2] = {0, 0};
+  int mode = 1;
+};
+constexpr uint32_t kPrefetchChunk = 4096;
 
 enum GemvEpilogue {
   EPI_STORE = 0,     // y = acc (+ resid)
@@ -45,14 +63,22 @@ struct GemvParams {
   // EPI_LOGITS
   float* part_val = nullptr;
   uint32_t* part_idx = nullptr;
+  PrefetchPlan pf;
+  uint32_t* err = nullptr;  // optional device word for error bits when there is no StepState (4 = a bounded wait gave up)
 };
 
 // Tunable launch shape of the GEMV family.
 struct GemvTune {
-  int rows_per_warp = 2;  // 1, 2 or 4 (EPI_QKV_ROPE and EPI_SILU_MUL need an even value)
-  int unroll = 4;         // 16-byte loads in flight per row per lane: 2, 4 or 8
+  int mode = 0;           // 0 = register double-buffered streamer, 1 = shared-memory ring fed by bulk copies
+  int rows_per_warp = 2;  // mode 0: 1, 2 or 4; mode 1: 1 or 2 (EPI_QKV_ROPE and EPI_SILU_MUL need an even value)
+  int unroll = 4;         // mode 0: 16-byte loads in flight per row per lane (2, 4 or 8); mode 1: ring stages (2, 3, 4, 6)
   int ctas_per_sm = 2;    // persistent grid = min(needed, 148 * ctas_per_sm) CTAs of 256 threads
 };
+
+size_t gemv_ring_smem(const GemvParams& p, int R, int S);
+uint32_t gemv_ring_grid(const GemvParams& p, int R, int ctas_per_sm);
+cudaError_t launch_gemv_ring(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue epi, const GemvParams& p, int R,
+                             int S, int ctas_per_sm, bool pdl);
 
 // Number of CTAs the launch will use (the LM head needs it to size its partial buffers).
 uint32_t gemv_grid(int wdtype, GemvEpilogue epi, const GemvParams& p, const GemvTune& t);
@@ -70,6 +96,7 @@ struct AttnParams {
   float* part = nullptr;       // [qH][S_max][d+2] split partials
   uint32_t* tickets = nullptr; // [kvH * head_groups], zero between launches
   uint32_t S_max = 1;
+  PrefetchPlan pf;
 };
 
 constexpr uint32_t kAttnMinChunk = 512;   // fewest positions one CTA takes before the range is split
@@ -81,12 +108,12 @@ size_t attn_part_floats(uint32_t qH, uint32_t d, uint32_t S_max);
 cudaError_t launch_attn_decode(cudaStream_t s, int kvdtype, const AttnParams& p, bool pdl);
 
 cudaError_t launch_embed(cudaStream_t s, int wdtype, const void* E, uint32_t H, uint32_t V, StepState* state,
-                         const uint32_t* prompt, uint32_t token_imm, float* x_out, bool pdl);
+                         const uint32_t* prompt, uint32_t token_imm, float* x_out, const PrefetchPlan& pf, bool pdl);
 // Reduce the LM head's per-CTA partials to the arg-max (lowest index among maxima), feed it back as the next
 // token and advance the position.
 cudaError_t launch_argmax_final(cudaStream_t s, const float* part_val, const uint32_t* part_idx, uint32_t nparts,
                                 StepState* state, uint32_t* argmax_out, uint32_t* history, uint32_t history_cap,
-                                bool pdl);
+                                const PrefetchPlan& pf, bool pdl);
 // Head-less prompt step: position and prompt cursor advance by one.
 cudaError_t launch_advance(cudaStream_t s, StepState* state, bool pdl);
 

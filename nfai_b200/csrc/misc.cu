@@ -24,7 +24,9 @@ cudaLaunchConfig_t make_cfg(dim3 grid, dim3 block, cudaStream_t s, cudaLaunchAtt
 // Token source: the prompt buffer at state->prompt_idx, else state->cur_token, else the immediate.
 template <typename WT>
 __global__ void embed_kernel(const WT* __restrict__ E, uint32_t H, uint32_t V, StepState* state,
-                             const uint32_t* __restrict__ prompt, uint32_t token_imm, float* __restrict__ x_out) {
+                             const uint32_t* __restrict__ prompt, uint32_t token_imm, float* __restrict__ x_out,
+                             const PrefetchPlan pf) {
+  prefetch_plan(pf, kPrefetchChunk);
   pdl_launch_dependents();
   pdl_wait();
   uint32_t tok = token_imm;
@@ -43,9 +45,10 @@ __global__ void embed_kernel(const WT* __restrict__ E, uint32_t H, uint32_t V, S
 __global__ void __launch_bounds__(256) argmax_final_kernel(const float* __restrict__ part_val,
                                                           const uint32_t* __restrict__ part_idx, uint32_t nparts,
                                                           StepState* state, uint32_t* argmax_out, uint32_t* history,
-                                                          uint32_t history_cap) {
+                                                          uint32_t history_cap, const PrefetchPlan pf) {
   __shared__ float sv[256];
   __shared__ uint32_t si[256];
+  prefetch_plan(pf, kPrefetchChunk);
   pdl_launch_dependents();
   pdl_wait();
   float bv = -INFINITY;
@@ -112,24 +115,24 @@ __global__ void ingest_kernel(const IngestParams p) {
 }  // namespace
 
 cudaError_t launch_embed(cudaStream_t s, int wdtype, const void* E, uint32_t H, uint32_t V, StepState* state,
-                         const uint32_t* prompt, uint32_t token_imm, float* x_out, bool pdl) {
+                         const uint32_t* prompt, uint32_t token_imm, float* x_out, const PrefetchPlan& pf, bool pdl) {
   cudaLaunchAttribute attr[1];
   uint32_t blocks = (H + 255) / 256;
   cudaLaunchConfig_t cfg = make_cfg(dim3(blocks), dim3(256), s, attr, pdl);
   if (wdtype == 1)
     return cudaLaunchKernelEx(&cfg, embed_kernel<__half>, reinterpret_cast<const __half*>(E), H, V, state, prompt,
-                              token_imm, x_out);
+                              token_imm, x_out, pf);
   return cudaLaunchKernelEx(&cfg, embed_kernel<float>, reinterpret_cast<const float*>(E), H, V, state, prompt,
-                            token_imm, x_out);
+                            token_imm, x_out, pf);
 }
 
 cudaError_t launch_argmax_final(cudaStream_t s, const float* part_val, const uint32_t* part_idx, uint32_t nparts,
                                 StepState* state, uint32_t* argmax_out, uint32_t* history, uint32_t history_cap,
-                                bool pdl) {
+                                const PrefetchPlan& pf, bool pdl) {
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t cfg = make_cfg(dim3(1), dim3(256), s, attr, pdl);
   return cudaLaunchKernelEx(&cfg, argmax_final_kernel, part_val, part_idx, nparts, state, argmax_out, history,
-                            history_cap);
+                            history_cap, pf);
 }
 
 cudaError_t launch_advance(cudaStream_t s, StepState* state, bool pdl) {

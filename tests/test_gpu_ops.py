@@ -53,18 +53,36 @@ def test_gemv(cuda_ctx, oracle, N, K, dtype, norm, resid):
     assert rel_err(host(y), want) < TOL
 
 
-@pytest.mark.parametrize("R,U", [(1, 2), (1, 8), (2, 2), (2, 8), (4, 2), (4, 4)])
-def test_gemv_launch_shapes(cuda_ctx, oracle, monkeypatch, R, U):
-    """Every tunable launch shape computes the same thing."""
-    monkeypatch.setenv("NFAI_TUNE_OP", f"{R},{U}")
-    rng = np.random.default_rng(R * 10 + U)
-    N, K = 203, 1544
-    W = (rng.standard_normal((N, K)) * 0.05).astype(np.float16)
+@pytest.mark.parametrize("shape", ["1,2,2,0", "1,8,2,0", "2,2,1,0", "2,8,4,0", "4,2,2,0", "4,4,2,0",
+                                   "1,2,1,1", "1,4,2,1", "1,6,1,1", "2,2,1,1", "2,3,1,1", "2,4,2,1"])
+@pytest.mark.parametrize("N,K,dtype", [(203, 1544, np.float16), (64, 256, np.float32), (1000, 2048, np.float16),
+                                       (37, 8192, np.float16), (5000, 520, np.float32)])
+def test_gemv_launch_shapes(cuda_ctx, oracle, monkeypatch, shape, N, K, dtype):
+    """Every tunable launch shape (rows per warp, depth, CTAs per SM, mode 0 = registers / 1 = shared-memory
+    ring fed by bulk copies) computes the same thing, through every epilogue."""
+    monkeypatch.setenv("NFAI_TUNE_OP", shape)
+    rng = np.random.default_rng(N + K)
+    W = (rng.standard_normal((N, K)) * 0.05).astype(dtype)
     x = rng.standard_normal(K).astype(np.float32)
-    dW, dx = dev(W), dev(x)
+    g = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    r = rng.standard_normal(N).astype(np.float32)
+    dW, dx, dg, dr = dev(W), dev(x), dev(g), dev(r)
     y = torch.empty(N, dtype=torch.float32, device="cuda")
-    call(cuda_ctx, "nfai_op_gemv", ptr(dW), _lib.F16, N, K, ptr(dx), None, C.c_float(0), None, ptr(y))
-    assert rel_err(host(y), oracle.matvec(x, W)) < TOL
+    call(cuda_ctx, "nfai_op_gemv", ptr(dW), dtype_code(dtype), N, K, ptr(dx), ptr(dg), C.c_float(1e-5), ptr(dr), ptr(y))
+    a = oracle.rmsnorm(x, g, 1e-5)
+    assert rel_err(host(y), oracle.matvec(a, W) + r) < TOL
+    # logits + arg-max through the same shape
+    logits = torch.empty(N, dtype=torch.float32, device="cuda")
+    am = torch.zeros(1, dtype=torch.int32, device="cuda")
+    call(cuda_ctx, "nfai_op_lm_head", ptr(dW), dtype_code(dtype), ptr(dx), ptr(dg), C.c_float(1e-5), K, N, ptr(logits), ptr(am))
+    got = host(logits)
+    assert rel_err(got, oracle.matvec(a, W)) < TOL
+    assert int(host(am)[0]) == oracle.argmax(got)
+    if N % 2 == 0:  # gate/up pairs
+        h = torch.empty(N // 2, dtype=torch.float32, device="cuda")
+        call(cuda_ctx, "nfai_op_ffn_gate_up", ptr(dW), dtype_code(dtype), ptr(dx), ptr(dg), C.c_float(1e-5), K, N // 2, ptr(h))
+        yy = oracle.matvec(a, W)
+        assert rel_err(host(h), oracle.silu_mul(yy[0::2], yy[1::2])) < TOL
 
 
 def rope_cs_table(oracle, ctx, rope_dim, theta):
