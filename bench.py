@@ -295,7 +295,10 @@ def main():
     ap.add_argument("--kv-dtype", default="f16", choices=["f16", "f32", "auto"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prompt-len", type=int, default=128, help="shorter prompts are for profiler captures only")
     args = ap.parse_args()
+    global PROMPT_LEN
+    PROMPT_LEN = args.prompt_len
     from nfai_b200 import synth
     cfg = synth.get_config(args.config)
     if args.impl == "reference":
