@@ -32,6 +32,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture
+# summarised in profiles/gemv_decode_llama1b_f16_ncu.md (configs[1], one GPU)
+NCU_TRAFFIC_BYTES = {("c1", 1): 67152128 + 350464}
 PROMPT_LEN = 128
 
 
@@ -263,7 +266,7 @@ def run_ours(args, cfg):
                 "same_tokens_as_device_loop": same_tokens},
         "gpu_launches": K * launches,
         "roofline": {"bound": "hbm", "kernel": "gemv_kernel (FFN gate/up + RMSNorm + SiLU*up)", "achieved": dom["gbs"],
-                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": None,
+                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": NCU_TRAFFIC_BYTES.get((args.config, world)),
                      "launch_us": dom["us"], "bytes_per_launch": dom["bytes"]},
         "step_roofline": {"bytes_per_token_per_gpu": step_bytes, "achieved_gbs": step_bytes / (ms / K * 1e-3) / 1e9,
                           "frac_of_8tbs": step_bytes / (ms / K * 1e-3) / 8e12,

@@ -1,0 +1,68 @@
+// The device side of LlamaModel: upload, prompt ingestion, decode. LlamaModel keeps its public shape
+// (NFAI.Models.Llama3/LlamaModel.cs:10-175) and holds one of these instead of the shader objects.
+using NFAI.Core;
+
+namespace NFAI.Cuda;
+
+public sealed unsafe class CudaLlamaBackend : IDisposable
+{
+    private readonly CudaContext ctx;
+    private IntPtr model;
+    public uint Vocab { get; }
+
+    public CudaLlamaBackend(CudaContext ctx, NfaiHParams hp)
+    {
+        this.ctx = ctx;
+        Vocab = hp.V;
+        Native.Check(Native.nfai_model_create(ctx.Handle, in hp, out model), ctx.Handle);
+    }
+
+    // Streams one tensor exactly as the reference does for a shader property: the chunks GetDataRaw yields
+    // (halves already widened to float32, NFAI.Core/AbstractComputeCollection.cs:36-79) go to the device.
+    public void Upload(AbstractComputeCollection tensor, IEnumerable<byte[]> rawChunks, bool chunksAreFloat32)
+    {
+        var shape = tensor.Shape.Select(s => (ulong)s).ToArray();
+        fixed (ulong* ps = shape)
+            Native.Check(Native.nfai_model_tensor_begin(model, tensor.Name, chunksAreFloat32 ? 0 : 1, ps, shape.Length), ctx.Handle);
+        foreach (var chunk in rawChunks)
+            fixed (byte* pb = chunk)
+                Native.Check(Native.nfai_model_tensor_chunk(model, pb, (nuint)chunk.Length), ctx.Handle);
+        Native.Check(Native.nfai_model_tensor_end(model), ctx.Handle);
+    }
+
+    public void FinalizeModel() => Native.Check(Native.nfai_model_finalize(model), ctx.Handle);
+
+    // Prompt loop of RunAsync (LlamaModel.cs:103-126); returns the logits of the last prompt token.
+    public float[] Prefill(ReadOnlySpan<uint> tokens)
+    {
+        var logits = new float[Vocab];
+        fixed (uint* pt = tokens) fixed (float* pl = logits)
+            Native.Check(Native.nfai_prefill(model, pt, tokens.Length, pl, null), ctx.Handle);
+        return logits;
+    }
+
+    // One iteration of the decode loop (LlamaModel.cs:134-173); logits go to SamplingUtils.TopP on the host.
+    public float[] Decode(uint token)
+    {
+        var logits = new float[Vocab];
+        fixed (float* pl = logits)
+            Native.Check(Native.nfai_decode(model, token, pl, null), ctx.Handle);
+        return logits;
+    }
+
+    // Greedy variant: only the arg-max index crosses PCIe (SamplingUtils.ArgMax semantics).
+    public uint DecodeGreedy(uint token)
+    {
+        uint am;
+        Native.Check(Native.nfai_decode(model, token, null, &am), ctx.Handle);
+        return am;
+    }
+
+    public void Reset() => Native.Check(Native.nfai_reset(model), ctx.Handle);
+
+    public void Dispose()
+    {
+        if (model != IntPtr.Zero) { Native.nfai_model_destroy(model); model = IntPtr.Zero; }
+        GC.SuppressFinalize(this);
+    }
+}
