@@ -240,6 +240,20 @@ int nfai_op_attn_decode(nfai_ctx* ctx, const float* q, const void* kcache, const
                         size_t scratch_bytes);
 size_t nfai_op_attn_scratch_bytes(uint32_t qH, uint32_t kvH, uint32_t d, uint32_t max_seq);
 
+/* Same computation as nfai_op_attn_decode, for callers that cannot allocate device memory where they run it (a
+ * host working inside a fixed device-memory budget, or a per-token loop that must avoid cudaMalloc's device-wide
+ * synchronisation): the split scratch is a 256 KiB array built into the library, so the call takes no scratch
+ * pointer and performs no allocation of any kind. Inputs and outputs are still the caller's device buffers.
+ *  - Geometries whose scratch (nfai_op_attn_scratch_bytes) exceeds 256 KiB are rejected with NFAI_ERR_ARG
+ *    (e.g. 32 query heads of dimension 128 over more than 9 216 positions).
+ *  - Every GPU on which the library is loaded holds those 256 KiB until the process exits.
+ *  - The first call on a device resolves the array's device address (a one-time set-up); make that first call
+ *    before any stream capture is begun.
+ *  - All calls share the one array: two calls whose GPU work overlaps (other streams, other threads) race on it.
+ * No counterpart in the reference. */
+int nfai_op_attn_decode_static(nfai_ctx* ctx, const float* q, const void* kcache, const void* vcache, int kv_dtype,
+                               uint32_t seq, uint32_t qH, uint32_t kvH, uint32_t d, float* out);
+
 /* logits = W * RMSNorm(x) (W[V][H]) and the lowest index of their maximum into *argmax_out (device).
  * replaces: output RMSNorm + LM-head MatrixMultiplyShader (LlamaModel.cs:58-67,160-163) and
  *           SamplingUtils.ArgMax (SamplingUtils.cs:55-56). */

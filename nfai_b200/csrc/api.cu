@@ -557,6 +557,13 @@ float half_bits_to_float(uint16_t h) { return __half2float(__ushort_as_half(h));
 
 }  // namespace
 
+// ---- context accessors for entry points that live in other translation units ---------------------------------
+namespace nfai {
+int ctx_device(const nfai_ctx* c) { return c->device; }
+cudaStream_t ctx_stream(const nfai_ctx* c) { return c->stream; }
+int ctx_fail(nfai_ctx* c, int code, const char* message) { return fail(c, code, "%s", message); }
+}  // namespace nfai
+
 // =============================================================================================================
 extern "C" {
 
