@@ -175,12 +175,8 @@ def run_ours(args, cfg):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        from nfai_b200 import CudaContext
-        buf = torch.zeros(128, dtype=torch.uint8, device="cuda")
-        if rank == 0:
-            buf.copy_(torch.frombuffer(bytearray(CudaContext.tp_unique_id()), dtype=torch.uint8))
-        dist.broadcast(buf, 0)
-        uid = bytes(buf.cpu().numpy().tobytes())
+        from nfai_b200 import CudaContext, tp
+        uid = tp.share_unique_id(dist, rank, CudaContext.tp_unique_id, device="cuda")
 
     def barrier():
         if dist is not None:

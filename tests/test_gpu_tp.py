@@ -1,0 +1,75 @@
+"""Tensor parallelism on 2 (and 4) GPUs: one process per GPU, logits against the CPU oracle and identical greedy
+tokens on every rank. Skipped on a single-GPU box."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank: int, world: int, port: int, key: str, out_q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+
+    from nfai_b200 import CudaContext, LlamaModel, LlamaModelFactory, synth, synthetic_tensors, tp
+    from oracle import oracle as O
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        uid = tp.share_unique_id(dist, rank, CudaContext.tp_unique_id)
+        cfg = synth.get_config(key, gain_std=0.1)
+        factory = LlamaModelFactory(rank, rank, world, uid)
+        model = LlamaModel(factory.ctx, synth.metadata(cfg), synthetic_tensors(cfg, 0), 48, kv_dtype="f32")
+        ref = O.OracleModel(cfg, ctx=48).load_synthetic(0)
+        toks = synth.prompt_ids(cfg, 12, 0)
+        worst = 0.0
+        for t in toks[:6]:
+            want = ref.decode(int(t))
+            got, am = model.decode(int(t))
+            assert am == O.argmax(got)
+            worst = max(worst, float(np.abs(got - want).max() / np.abs(want).max()))
+        want = None
+        for t in toks[6:]:
+            want = ref.decode(int(t))
+        got, am = model.prefill(toks[6:])
+        worst = max(worst, float(np.abs(got - want).max() / np.abs(want).max()))
+        greedy, _ = model.decode_greedy(am, 8)
+        tk, exp = am, []
+        for _ in range(8):
+            tk = O.argmax(ref.decode(tk))
+            exp.append(tk)
+        out_q.put((rank, worst, list(map(int, greedy)), exp, cfg.dtype))
+        dist.barrier()
+        model.Dispose()
+        factory.Dispose()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,key", [(2, "c0"), (2, "s1"), (4, "s1")])
+def test_tensor_parallel_matches_oracle(world, key):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29700 + (os.getpid() + world * 7) % 2000
+    procs = [ctx.Process(target=_worker, args=(r, world, port, key, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    res.sort()
+    for rank, worst, greedy, exp, dtype in res:
+        assert worst <= (1e-4 if dtype == "f32" else 2e-3), (rank, worst)
+        assert greedy == res[0][2]          # every rank generated the same tokens
+        if dtype == "f32":
+            assert greedy == exp
