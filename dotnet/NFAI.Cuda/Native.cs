@@ -42,6 +42,8 @@ internal static unsafe partial class Native
     [DllImport(Lib)] internal static extern int nfai_read_hidden(IntPtr model, uint layer, float* outHidden);
     [DllImport(Lib)] internal static extern int nfai_model_tune(IntPtr model, int which, int mode, int rowsPerWarp, int depth, int ctasPerSm);
     [DllImport(Lib)] internal static extern int nfai_model_set_prefetch(IntPtr model, ulong lookaheadBytes, ulong extraBytes, int mode);
+    [DllImport(Lib)] internal static extern int nfai_model_set_fused_step(IntPtr model, int enabled);
+    [DllImport(Lib)] internal static extern int nfai_op_attn_decode_static(IntPtr ctx, float* q, void* kcache, void* vcache, int kvDType, uint seq, uint qH, uint kvH, uint d, float* outp);
     [DllImport(Lib)] internal static extern int nfai_profile_kernel(IntPtr model, int which, int iters, out float avgMs, out ulong bytesPerLaunch);
     [DllImport(Lib)] internal static extern int nfai_step_launches(IntPtr model, out int launches);
 

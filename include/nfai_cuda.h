@@ -196,6 +196,17 @@ int nfai_model_tune(nfai_model* m, int which, int mode, int rows_per_warp, int d
  * No counterpart in the reference. */
 int nfai_model_set_prefetch(nfai_model* m, uint64_t lookahead_bytes, uint64_t extra_bytes, int mode);
 
+/* Run the decode step as ONE persistent kernel (grid barriers between its phases, the next phase's weights
+ * requested before each barrier) instead of 3 + 5L kernels. Same arithmetic, same results. Available on one GPU when
+ * the whole grid is co-resident; enabled != 0 switches it on and captures the decode graphs again.
+ * No counterpart in the reference (it submits and waits for every dispatch: ShaderWrapper.cs:208-245). */
+int nfai_model_set_fused_step(nfai_model* m, int enabled);
+
+/* Diagnostics of the fused step: with NFAI_TRACE=1 in the environment at nfai_model_finalize, CTA 0 records a
+ * %globaltimer value (nanoseconds) at every phase end and barrier of the last step; this copies up to `capacity`
+ * of them out. No counterpart in the reference. */
+int nfai_model_trace(nfai_model* m, uint64_t* ns_out, int capacity, int* count);
+
 /* Number of kernel launches inside one decode step (the captured graph's kernel nodes). */
 int nfai_step_launches(const nfai_model* m, int* out);
 

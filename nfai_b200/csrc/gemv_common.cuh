@@ -54,7 +54,7 @@ __device__ __forceinline__ void row_epilogue(const GemvParams& p, uint32_t row0,
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       uint32_t n = row0 + r;
-      if (n < p.N) p.y[n] = p.resid ? p.resid[n] + acc[r] : acc[r];
+      if (n < p.N) p.y[n] = p.resid ? __ldcg(p.resid + n) + acc[r] : acc[r];
     }
   } else if constexpr (EPI == EPI_QKV_ROPE) {
     static_assert(R % 2 == 0, "RoPE pairs adjacent rows");

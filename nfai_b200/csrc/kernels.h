@@ -36,6 +36,7 @@ struct PrefetchPlan {
 };
 constexpr uint32_t kPrefetchChunk = 4096;
 
+
 enum GemvEpilogue {
   EPI_STORE = 0,     // y = acc (+ resid)
   EPI_QKV_ROPE = 1,  // rows are [Q | K | V]; RoPE on Q and K; K,V rows go to the cache at row pos
@@ -96,14 +97,21 @@ struct AttnParams {
   float* part = nullptr;       // [qH][S_max][d+2] split partials
   uint32_t* tickets = nullptr; // [kvH * head_groups], zero between launches
   uint32_t S_max = 1;
+  // Launch shape: query heads that share one pass over K and V (4 = every head of a Llama-3 KV group: K and V
+  // are read once, right for long contexts; 1 = one CTA per query head: four times the CTAs and all of a short
+  // context in flight at once) and the fewest positions a CTA takes before the range is split.
+  uint32_t heads_per_cta = 4;  // 4, 2 or 1
+  uint32_t min_chunk = 512;
   PrefetchPlan pf;
 };
+
 
 constexpr uint32_t kAttnMinChunk = 512;   // fewest positions one CTA takes before the range is split
 constexpr uint32_t kAttnHeadsPerCta = 4;  // query heads sharing one pass over K/V
 
-uint32_t attn_head_groups(uint32_t qH, uint32_t kvH);
-uint32_t attn_splits(uint32_t qH, uint32_t kvH, uint32_t max_seq);
+uint32_t attn_head_groups(uint32_t qH, uint32_t kvH, uint32_t heads_per_cta = kAttnHeadsPerCta);
+uint32_t attn_splits(uint32_t qH, uint32_t kvH, uint32_t max_seq, uint32_t heads_per_cta = kAttnHeadsPerCta,
+                     uint32_t min_chunk = kAttnMinChunk);
 size_t attn_part_floats(uint32_t qH, uint32_t d, uint32_t S_max);
 cudaError_t launch_attn_decode(cudaStream_t s, int kvdtype, const AttnParams& p, bool pdl);
 
