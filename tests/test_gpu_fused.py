@@ -50,7 +50,8 @@ def test_fused_step_matches_per_kernel_path_and_oracle(factory, oracle, key, ove
     for l in range(cfg.L):
         ka, va = a.read_kv(l, n - 1)
         kb, vb = b.read_kv(l, n - 1)
-        assert np.allclose(ka, kb, atol=1e-5) and np.allclose(va, vb, atol=1e-5)
+        kv_tol = 1e-5 if kv == "f32" else 2e-3  # a float16 cache row may round the other way by one ulp
+        assert rel_err(kb, ka) <= kv_tol and rel_err(vb, va) <= kv_tol
         assert rel_err(b.read_hidden(l), a.read_hidden(l)) <= 1e-4
     b.set_fused_step(False)
     assert b.step_launches() == 3 + 5 * cfg.L
