@@ -186,6 +186,13 @@ def run_ours(args, cfg):
     K, W = args.steps, max(args.warmup, 3)
     ctx_size = PROMPT_LEN + W + K + 8
     factory = LlamaModelFactory(local_rank, rank, world, uid)
+    exchange = "none"
+    if world > 1:
+        exchange = "nccl"
+        if not args.nccl_allreduce:
+            from nfai_b200 import tp as _tp
+            _tp.connect_peers(dist, factory.ctx, device="cuda")
+            exchange = "peer-memory push all-reduce (own kernel over NVLink)"
     t_load = time.perf_counter()
     model = LlamaModel(factory.ctx, synth.metadata(cfg), synthetic_tensors(cfg, args.seed), ctx_size,
                        kv_dtype=args.kv_dtype)
@@ -255,7 +262,7 @@ def run_ours(args, cfg):
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32 accumulate over " + cfg.dtype + " weights", "data": "synthetic",
         "config": {"workload": workload_name(args.config, cfg, K), "weights": cfg.dtype, "kv_cache": model.kv_dtype,
-                   "parallelism": f"tp{world}", "l2": "inputs larger than L2: every step streams all weights "
+                   "parallelism": f"tp{world}", "exchange": exchange, "l2": "inputs larger than L2: every step streams all weights "
                    f"({cfg.streamed_matrix_params() * 2 / 1e9:.2f} GB at TP1) against a 126 MB L2",
                    "seed": args.seed},
         "e2e": {"value": K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 32,
@@ -294,6 +301,7 @@ def main():
     ap.add_argument("--kv-dtype", default="f16", choices=["f16", "f32", "auto"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--nccl-allreduce", action="store_true", help="N > 1: use NCCL all-reduces instead of the peer-memory kernel")
     ap.add_argument("--prompt-len", type=int, default=128, help="shorter prompts are for profiler captures only")
     args = ap.parse_args()
     global PROMPT_LEN

@@ -24,6 +24,8 @@ internal static unsafe partial class Native
     [DllImport(Lib)] internal static extern int nfai_ctx_create(int deviceOrdinal, out IntPtr ctx);
     [DllImport(Lib)] internal static extern int nfai_tp_unique_id(byte* outId, nuint outBytes);
     [DllImport(Lib)] internal static extern int nfai_ctx_create_tp(int deviceOrdinal, int rank, int world, byte* uid, nuint uidBytes, out IntPtr ctx);
+    [DllImport(Lib)] internal static extern int nfai_tp_export_peer(IntPtr ctx, byte* outDesc, nuint outBytes);
+    [DllImport(Lib)] internal static extern int nfai_tp_import_peers(IntPtr ctx, byte* descs, int n);
     [DllImport(Lib)] internal static extern int nfai_ctx_destroy(IntPtr ctx);
     [DllImport(Lib)] internal static extern int nfai_model_create(IntPtr ctx, in NfaiHParams hp, out IntPtr model);
     [DllImport(Lib, CharSet = CharSet.Ansi)] internal static extern int nfai_model_tensor_begin(IntPtr model, string ggufName, int srcDType, ulong* shape, int ndim);
@@ -43,6 +45,7 @@ internal static unsafe partial class Native
     [DllImport(Lib)] internal static extern int nfai_model_tune(IntPtr model, int which, int mode, int rowsPerWarp, int depth, int ctasPerSm);
     [DllImport(Lib)] internal static extern int nfai_model_set_prefetch(IntPtr model, ulong lookaheadBytes, ulong extraBytes, int mode);
     [DllImport(Lib)] internal static extern int nfai_model_set_fused_step(IntPtr model, int enabled);
+    [DllImport(Lib)] internal static extern int nfai_model_trace(IntPtr model, ulong* nsOut, int capacity, out int count);
     [DllImport(Lib)] internal static extern int nfai_op_attn_decode_static(IntPtr ctx, float* q, void* kcache, void* vcache, int kvDType, uint seq, uint qH, uint kvH, uint d, float* outp);
     [DllImport(Lib)] internal static extern int nfai_profile_kernel(IntPtr model, int which, int iters, out float avgMs, out ulong bytesPerLaunch);
     [DllImport(Lib)] internal static extern int nfai_step_launches(IntPtr model, out int launches);

@@ -88,6 +88,14 @@ int nfai_tp_unique_id(void* out, size_t out_bytes);
 int nfai_ctx_create_tp(int device_ordinal, int rank, int world, const void* nccl_uid, size_t uid_bytes,
                        nfai_ctx** out);
 
+/* Optional, before nfai_model_finalize: let the tensor-parallel ranks exchange partial sums through each other's
+ * memory over NVLink with this library's own kernel instead of NCCL all-reduces. Every rank writes a 128-byte
+ * descriptor of its exchange area (nfai_tp_export_peer), the host gathers the `world` descriptors in rank order
+ * and gives the array to every rank (nfai_tp_import_peers). Works across processes (CUDA IPC) and across threads
+ * of one process (peer access). No counterpart in the reference (single device). */
+int nfai_tp_export_peer(nfai_ctx* ctx, void* out, size_t out_bytes);
+int nfai_tp_import_peers(nfai_ctx* ctx, const void* descs, int n);
+
 /* replaces: LlamaModelFactory.Dispose (LlamaModelFactory.cs:24-32). */
 int nfai_ctx_destroy(nfai_ctx* ctx);
 

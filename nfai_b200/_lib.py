@@ -46,6 +46,8 @@ SIGNATURES = {
     "nfai_ctx_create": (_i, [_i, _pp]),
     "nfai_tp_unique_id": (_i, [_vp, _sz]),
     "nfai_ctx_create_tp": (_i, [_i, _i, _i, _vp, _sz, _pp]),
+    "nfai_tp_export_peer": (_i, [_vp, _vp, _sz]),
+    "nfai_tp_import_peers": (_i, [_vp, _vp, _i]),
     "nfai_ctx_destroy": (_i, [_vp]),
     "nfai_model_create": (_i, [_vp, C.POINTER(HParams), _pp]),
     "nfai_model_tensor_begin": (_i, [_vp, C.c_char_p, _i, C.POINTER(C.c_uint64), _i]),

@@ -49,6 +49,16 @@ class CudaContext:
         check(_lib.load().nfai_tp_unique_id(buf, 128))
         return buf.raw
 
+    def export_peer(self) -> bytes:
+        buf = C.create_string_buffer(128)
+        check(_lib.load().nfai_tp_export_peer(self.handle, buf, 128), self.handle)
+        return buf.raw
+
+    def import_peers(self, descs: bytes):
+        n = len(descs) // 128
+        buf = C.create_string_buffer(descs, len(descs))
+        check(_lib.load().nfai_tp_import_peers(self.handle, buf, n), self.handle)
+
     def close(self):
         if self.handle:
             _lib.load().nfai_ctx_destroy(self.handle)

@@ -385,7 +385,7 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     go.pf = pp.next(end_of(LW.o), true);
     STEP(launch_gemv(s, wdt, kvdt, EPI_STORE, go, m->tune_o, pdl));
     if (c->world > 1) {
-      e = tp_allreduce_residual(c->tp, s, m->tp_buf, x_in(m, l), x_mid(m, l), hp.H, &n);
+      e = tp_allreduce_residual(c->tp, s, m->tp_buf, x_in(m, l), x_mid(m, l), hp.H, m->state, 2 * l, &n);
       if (e != cudaSuccess) return e;
     }
     GemvParams gg = gateup_params(m, l);
@@ -395,7 +395,7 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     gd.pf = pp.next(pp.off(LW.ffn_norm.ptr) + (uint64_t)hp.H * 4, true);
     STEP(launch_gemv(s, wdt, kvdt, EPI_STORE, gd, m->tune_down, pdl));
     if (c->world > 1) {
-      e = tp_allreduce_residual(c->tp, s, m->tp_buf, x_mid(m, l), x_in(m, l + 1), hp.H, &n);
+      e = tp_allreduce_residual(c->tp, s, m->tp_buf, x_mid(m, l), x_in(m, l + 1), hp.H, m->state, 2 * l + 1, &n);
       if (e != cudaSuccess) return e;
     }
   }
@@ -408,9 +408,10 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
       if (e != cudaSuccess) return e;
     }
     STEP(launch_argmax_final(s, m->part_val, m->part_idx, c->world > 1 ? (uint32_t)c->world : m->nparts, m->state,
-                             nullptr, m->history, hp.ctx, pp.next(pp.total(), false), pdl && c->world == 1));
+                             nullptr, m->history, hp.ctx, pp.next(pp.total(), false), c->world > 1 ? tp_epoch_ptr(c->tp) : nullptr, 2 * hp.L,
+                             pdl && c->world == 1));
   } else {
-    STEP(launch_advance(s, m->state, pdl && c->world == 1));
+    STEP(launch_advance(s, m->state, c->world > 1 ? tp_epoch_ptr(c->tp) : nullptr, 2 * hp.L, pdl && c->world == 1));
   }
 #undef STEP
   if (launches) *launches = n;
@@ -656,6 +657,21 @@ int nfai_tp_unique_id(void* out, size_t out_bytes) {
 int nfai_ctx_create_tp(int device_ordinal, int rank, int world, const void* nccl_uid, size_t uid_bytes, nfai_ctx** out) {
   if (world > 1 && (!nccl_uid || uid_bytes < 128)) return fail(nullptr, NFAI_ERR_ARG, "nccl_uid must hold 128 bytes");
   return ctx_create_common(device_ordinal, rank, world, nccl_uid, uid_bytes, out);
+}
+
+int nfai_tp_export_peer(nfai_ctx* c, void* out, size_t out_bytes) {
+  if (!c) return fail(nullptr, NFAI_ERR_ARG, "ctx is null");
+  if (!c->tp) return fail(c, NFAI_ERR_STATE, "not a tensor-parallel context");
+  CU(c, cudaSetDevice(c->device));
+  int rc = tp_export_peer_desc(c->tp, out, out_bytes, c->err);
+  return rc;
+}
+
+int nfai_tp_import_peers(nfai_ctx* c, const void* descs, int n) {
+  if (!c) return fail(nullptr, NFAI_ERR_ARG, "ctx is null");
+  if (!c->tp) return fail(c, NFAI_ERR_STATE, "not a tensor-parallel context");
+  CU(c, cudaSetDevice(c->device));
+  return tp_import_peer_descs(c->tp, descs, n, c->err);
 }
 
 int nfai_ctx_destroy(nfai_ctx* c) {
@@ -1426,7 +1442,7 @@ int nfai_op_lm_head(nfai_ctx* c, const void* W, int dtype, const float* x, const
   p.part_val = pv;
   p.part_idx = (uint32_t*)(pv + nparts);
   cudaError_t e = launch_gemv(c->stream, dtype, NFAI_F32, EPI_LOGITS, p, t, false);
-  if (e == cudaSuccess) e = launch_argmax_final(c->stream, p.part_val, p.part_idx, nparts, nullptr, argmax_out, nullptr, 0, PrefetchPlan(), false);
+  if (e == cudaSuccess) e = launch_argmax_final(c->stream, p.part_val, p.part_idx, nparts, nullptr, argmax_out, nullptr, 0, PrefetchPlan(), nullptr, 0, false);
   cudaFreeAsync(pv, c->stream);
   return op_end(c, e);
 }

@@ -22,7 +22,7 @@ struct StepState {
   uint32_t prompt_idx;  // cursor into the prompt buffer for head-less prompt steps
   uint32_t last_argmax; // arg-max of the last step that ran the LM head
   uint32_t err;         // sticky error bits: 1 = token id out of range, 2 = position beyond the cache
-  uint32_t steps;       // number of steps executed (diagnostics)
+  uint32_t steps;       // index of the next history slot (reset by nfai_decode_greedy)
   uint32_t pad[2];
 };
 
@@ -121,9 +121,10 @@ cudaError_t launch_embed(cudaStream_t s, int wdtype, const void* E, uint32_t H, 
 // token and advance the position.
 cudaError_t launch_argmax_final(cudaStream_t s, const float* part_val, const uint32_t* part_idx, uint32_t nparts,
                                 StepState* state, uint32_t* argmax_out, uint32_t* history, uint32_t history_cap,
-                                const PrefetchPlan& pf, bool pdl);
+                                const PrefetchPlan& pf, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl);
 // Head-less prompt step: position and prompt cursor advance by one.
-cudaError_t launch_advance(cudaStream_t s, StepState* state, bool pdl);
+// xchg_epoch (may be null) counts the tensor-parallel exchanges completed on this context; a step adds its own.
+cudaError_t launch_advance(cudaStream_t s, StepState* state, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl);
 
 // Scatter/convert one uploaded chunk into a matrix's final place: source element g = elem_off + e sits at
 // (row, col) = (g / K, g % K); rows [row_lo,row_hi) x cols [col_lo,col_hi) are kept and land at

@@ -45,7 +45,8 @@ __global__ void embed_kernel(const WT* __restrict__ E, uint32_t H, uint32_t V, S
 __global__ void __launch_bounds__(256) argmax_final_kernel(const float* __restrict__ part_val,
                                                           const uint32_t* __restrict__ part_idx, uint32_t nparts,
                                                           StepState* state, uint32_t* argmax_out, uint32_t* history,
-                                                          uint32_t history_cap, const PrefetchPlan pf) {
+                                                          uint32_t history_cap, const PrefetchPlan pf,
+                                                          uint32_t* xchg_epoch, uint32_t xchg_per_step) {
   __shared__ float sv[256];
   __shared__ uint32_t si[256];
   prefetch_plan(pf, kPrefetchChunk);
@@ -86,16 +87,18 @@ __global__ void __launch_bounds__(256) argmax_final_kernel(const float* __restri
       state->cur_token = best;  // greedy feedback: the next step embeds this token unless the host overwrites it
       state->pos += 1;
       state->steps += 1;
+      if (xchg_epoch) *xchg_epoch += xchg_per_step;
     }
   }
 }
 
-__global__ void advance_kernel(StepState* state) {
+__global__ void advance_kernel(StepState* state, uint32_t* xchg_epoch, uint32_t xchg_per_step) {
   pdl_launch_dependents();
   pdl_wait();
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     state->pos += 1;
     state->prompt_idx += 1;
+    if (xchg_epoch) *xchg_epoch += xchg_per_step;
   }
 }
 
@@ -128,17 +131,17 @@ cudaError_t launch_embed(cudaStream_t s, int wdtype, const void* E, uint32_t H, 
 
 cudaError_t launch_argmax_final(cudaStream_t s, const float* part_val, const uint32_t* part_idx, uint32_t nparts,
                                 StepState* state, uint32_t* argmax_out, uint32_t* history, uint32_t history_cap,
-                                const PrefetchPlan& pf, bool pdl) {
+                                const PrefetchPlan& pf, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl) {
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t cfg = make_cfg(dim3(1), dim3(256), s, attr, pdl);
   return cudaLaunchKernelEx(&cfg, argmax_final_kernel, part_val, part_idx, nparts, state, argmax_out, history,
-                            history_cap, pf);
+                            history_cap, pf, xchg_epoch, xchg_per_step);
 }
 
-cudaError_t launch_advance(cudaStream_t s, StepState* state, bool pdl) {
+cudaError_t launch_advance(cudaStream_t s, StepState* state, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl) {
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t cfg = make_cfg(dim3(1), dim3(32), s, attr, pdl);
-  return cudaLaunchKernelEx(&cfg, advance_kernel, state);
+  return cudaLaunchKernelEx(&cfg, advance_kernel, state, xchg_epoch, xchg_per_step);
 }
 
 cudaError_t launch_ingest(cudaStream_t s, int src_dtype, int dst_dtype, const IngestParams& p) {

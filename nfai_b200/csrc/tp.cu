@@ -5,6 +5,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 #include <string.h>
+#include <unistd.h>
 
 #include "../../include/nfai_cuda.h"
 #include "common.cuh"
@@ -105,13 +106,102 @@ __global__ void unpack_pairs_kernel(const uint2* __restrict__ pairs, int world, 
 
 }  // namespace
 
+// Peer-memory exchange area of one rank, written by every rank (this one included) over NVLink:
+//   slots[parity][src][kPushMaxH] float32 partial sums, flags[src] = epoch of the last exchange src has delivered.
+constexpr uint32_t kPushMaxH = 16384;
+constexpr int kPushMaxWorld = 8;
+constexpr size_t kPushSlotFloats = (size_t)2 * kPushMaxWorld * kPushMaxH;
+constexpr size_t kPushBytes = kPushSlotFloats * 4 + 512;  // slots, 256 bytes of flags, 256 bytes local (epoch word)
+
+struct PushView {
+  float* slots[kPushMaxWorld];     // slot area of every rank (own entry = local pointer)
+  uint32_t* flags[kPushMaxWorld];  // flag words of every rank
+  int rank, world;
+};
+
+struct PeerDesc {  // 128 bytes on the wire
+  int32_t pid;
+  int32_t device;
+  uint64_t ptr;
+  cudaIpcMemHandle_t handle;  // 64 bytes
+  char pad[kTpPeerDescBytes - 16 - sizeof(cudaIpcMemHandle_t)];
+};
+static_assert(sizeof(PeerDesc) == kTpPeerDescBytes, "descriptor layout");
+
 struct TpComm {
   int device = 0, rank = 0, world = 1;
   ncclComm_t comm = nullptr;
   uint2* pairs = nullptr;       // [world]
   float* full_logits = nullptr; // [world * Vl], allocated on first use
   size_t full_logits_elems = 0;
+  char* push_local = nullptr;   // this rank's exchange area (its own cudaMalloc: it is exported whole)
+  void* push_opened[kPushMaxWorld] = {};  // IPC mappings to close
+  PushView view{};
+  bool push_ready = false;
 };
+
+namespace {
+
+constexpr unsigned long long kPushWaitNs = 1000000000ull;
+
+__device__ __forceinline__ unsigned long long tp_global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// One-shot push all-reduce + residual add, one CTA. Every rank stores its partial vector into its slot on every
+// rank, publishes the exchange's epoch with a system-scope release, waits (bounded) until every rank's epoch has
+// arrived in its own flags, then sums the slots in rank order -- the same order on every rank, so all ranks hold
+// bit-identical residual streams.
+__global__ void __launch_bounds__(1024) push_allreduce_residual_kernel(PushView pv, const float* __restrict__ partial,
+                                                                      const float* __restrict__ resid,
+                                                                      float* __restrict__ x_out, uint32_t H,
+                                                                      StepState* state, const uint32_t* epoch_base,
+                                                                      uint32_t index_in_step) {
+  __shared__ uint32_t s_ok;
+  const uint32_t epoch = *epoch_base + index_in_step + 1;
+  const uint32_t parity = epoch & 1u;
+  const int tid = threadIdx.x;
+  if (tid == 0) s_ok = 1;
+  for (uint32_t i = tid; i < H; i += blockDim.x) {
+    const float v = partial[i];
+    for (int dst = 0; dst < pv.world; ++dst)
+      pv.slots[dst][((size_t)parity * kPushMaxWorld + pv.rank) * kPushMaxH + i] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < pv.world) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pv.flags[tid] + pv.rank), "r"(epoch) : "memory");
+    // wait for rank `tid`'s epoch in this rank's own flags
+    const uint32_t* f = pv.flags[pv.rank] + tid;
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+    if ((int32_t)(seen - epoch) < 0) {
+      const unsigned long long t0 = tp_global_ns();
+      uint32_t polls = 0;
+      while (true) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+        if ((int32_t)(seen - epoch) >= 0) break;
+        if ((++polls & 63u) == 0 && tp_global_ns() - t0 > kPushWaitNs) {
+          s_ok = 0;
+          atomicOr(&state->err, 4u);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const float* mine = pv.slots[pv.rank] + (size_t)parity * kPushMaxWorld * kPushMaxH;
+  for (uint32_t i = tid; i < H; i += blockDim.x) {
+    float sum = 0.f;
+    for (int src = 0; src < pv.world; ++src) sum += __ldcg(mine + (size_t)src * kPushMaxH + i);
+    x_out[i] = resid[i] + sum;
+  }
+}
+
+}  // namespace
 
 int tp_unique_id(void* out, size_t out_bytes, std::string& err) {
   if (!out || out_bytes < sizeof(ncclUniqueId)) {
@@ -149,7 +239,9 @@ int tp_create(TpComm** out, int device, int rank, int world, const void* uid, si
     delete tp;
     return NFAI_ERR_NCCL;
   }
-  cudaError_t e = cudaMalloc((void**)&tp->pairs, sizeof(uint2) * 8);
+  cudaError_t e = cudaMalloc((void**)&tp->push_local, kPushBytes);  // own allocation: it is exported whole
+  if (e == cudaSuccess) e = cudaMemset(tp->push_local, 0, kPushBytes);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&tp->pairs, sizeof(uint2) * 8);
   if (e != cudaSuccess) {
     err = std::string("cudaMalloc: ") + cudaGetErrorString(e);
     g_nccl.CommDestroy(tp->comm);
@@ -162,6 +254,9 @@ int tp_create(TpComm** out, int device, int rank, int world, const void* uid, si
 
 void tp_destroy(TpComm* tp) {
   if (!tp) return;
+  for (int i = 0; i < kPushMaxWorld; ++i)
+    if (tp->push_opened[i]) cudaIpcCloseMemHandle(tp->push_opened[i]);
+  if (tp->push_local) cudaFree(tp->push_local);
   if (tp->comm) g_nccl.CommDestroy(tp->comm);
   if (tp->pairs) cudaFree(tp->pairs);
   if (tp->full_logits) cudaFree(tp->full_logits);
@@ -169,7 +264,13 @@ void tp_destroy(TpComm* tp) {
 }
 
 cudaError_t tp_allreduce_residual(TpComm* tp, cudaStream_t s, float* buf, const float* resid, float* x_out, uint32_t H,
-                                  int* launches) {
+                                  StepState* state, uint32_t index_in_step, int* launches) {
+  if (tp->push_ready && H <= kPushMaxH) {
+    push_allreduce_residual_kernel<<<1, 1024, 0, s>>>(tp->view, buf, resid, x_out, H, state, tp_epoch_ptr(tp),
+                                                       index_in_step);
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+  }
   ncclResult_t r = g_nccl.AllReduce(buf, buf, H, ncclFloat, ncclSum, tp->comm, s);
   if (r != ncclSuccess) return cudaErrorUnknown;
   add_residual_kernel<<<(H + 255) / 256, 256, 0, s>>>(buf, resid, x_out, H);
@@ -187,6 +288,73 @@ cudaError_t tp_gather_argmax(TpComm* tp, cudaStream_t s, float* part_val, uint32
   unpack_pairs_kernel<<<1, 32, 0, s>>>(tp->pairs, tp->world, part_val, part_idx);
   if (launches) *launches += 2;
   return cudaGetLastError();
+}
+
+uint32_t* tp_epoch_ptr(TpComm* tp) { return reinterpret_cast<uint32_t*>(tp->push_local + kPushSlotFloats * 4 + 256); }
+
+int tp_export_peer_desc(TpComm* tp, void* out, size_t out_bytes, std::string& err) {
+  if (!out || out_bytes < kTpPeerDescBytes) {
+    err = "peer descriptor buffer must hold 128 bytes";
+    return NFAI_ERR_ARG;
+  }
+  PeerDesc d;
+  memset(&d, 0, sizeof d);
+  d.pid = (int32_t)getpid();
+  d.device = tp->device;
+  d.ptr = (uint64_t)(uintptr_t)tp->push_local;
+  cudaError_t e = cudaIpcGetMemHandle(&d.handle, tp->push_local);
+  if (e != cudaSuccess) {
+    err = std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(e);
+    return NFAI_ERR_CUDA;
+  }
+  memcpy(out, &d, sizeof d);
+  return NFAI_OK;
+}
+
+int tp_import_peer_descs(TpComm* tp, const void* descs, int n, std::string& err) {
+  if (!descs || n != tp->world) {
+    err = "one peer descriptor per rank is needed";
+    return NFAI_ERR_ARG;
+  }
+  const PeerDesc* d = reinterpret_cast<const PeerDesc*>(descs);
+  PushView v{};
+  v.rank = tp->rank;
+  v.world = tp->world;
+  for (int r = 0; r < n; ++r) {
+    char* base = nullptr;
+    if (r == tp->rank) {
+      base = tp->push_local;
+    } else if (d[r].pid == (int32_t)getpid()) {
+      // same process, another device: plain peer access to the other context's allocation
+      int can = 0;
+      cudaDeviceCanAccessPeer(&can, tp->device, d[r].device);
+      if (!can) {
+        err = "no peer access between the devices";
+        return NFAI_ERR_CUDA;
+      }
+      cudaError_t e = cudaDeviceEnablePeerAccess(d[r].device, 0);
+      if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
+        err = std::string("cudaDeviceEnablePeerAccess: ") + cudaGetErrorString(e);
+        return NFAI_ERR_CUDA;
+      }
+      cudaGetLastError();
+      base = (char*)(uintptr_t)d[r].ptr;
+    } else {
+      void* p = nullptr;
+      cudaError_t e = cudaIpcOpenMemHandle(&p, d[r].handle, cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess) {
+        err = std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e);
+        return NFAI_ERR_CUDA;
+      }
+      tp->push_opened[r] = p;
+      base = (char*)p;
+    }
+    v.slots[r] = reinterpret_cast<float*>(base);
+    v.flags[r] = reinterpret_cast<uint32_t*>(base + kPushSlotFloats * 4);
+  }
+  tp->view = v;
+  tp->push_ready = true;
+  return NFAI_OK;
 }
 
 int tp_allgather_logits(TpComm* tp, cudaStream_t s, const float* logits_local, uint32_t Vl, float* host_out,

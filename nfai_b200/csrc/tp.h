@@ -7,6 +7,8 @@
 
 #include <string>
 
+#include "kernels.h"
+
 namespace nfai {
 
 struct TpComm;
@@ -18,8 +20,20 @@ void tp_destroy(TpComm* tp);
 
 // buf[0..H) holds this rank's partial sums; afterwards x_out = resid + sum over ranks (identical on every rank).
 // *launches is advanced by the number of kernels of this library that were enqueued.
+// Device word counting the exchanges completed on this context (advanced by the last kernel of every step).
+uint32_t* tp_epoch_ptr(TpComm* tp);
+
+// `index_in_step` numbers the exchanges of one step (0 .. 2L-1); together with the context's epoch word it gives every
+// exchange of the run its own epoch, which is what the peer-memory path uses as its flag value.
 cudaError_t tp_allreduce_residual(TpComm* tp, cudaStream_t s, float* buf, const float* resid, float* x_out, uint32_t H,
-                                  int* launches);
+                                  StepState* state, uint32_t index_in_step, int* launches);
+
+// Peer-memory exchange buffers. Every rank exports a 128-byte descriptor of its buffer (process id, device
+// pointer, CUDA IPC handle); the host gathers the descriptors of all ranks and hands them to every rank. After the
+// import the all-reduce runs as this library's own kernel over NVLink stores instead of an NCCL call.
+constexpr size_t kTpPeerDescBytes = 128;
+int tp_export_peer_desc(TpComm* tp, void* out, size_t out_bytes, std::string& err);
+int tp_import_peer_descs(TpComm* tp, const void* descs, int n, std::string& err);
 
 // part_val/part_idx hold nparts per-CTA arg-max partials with rank-local row indices; afterwards entries
 // [0, world) hold one (max, global lowest index) pair per rank, on every rank.

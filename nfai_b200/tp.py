@@ -54,3 +54,14 @@ def share_unique_id(dist, rank: int, make_uid: Callable[[], bytes], device: Opti
         buf.copy_(torch.frombuffer(bytearray(uid), dtype=torch.uint8))
     dist.broadcast(buf, 0)
     return bytes(buf.cpu().numpy().tobytes())
+
+
+def connect_peers(dist, ctx, device: Optional[str] = None) -> None:
+    """Gather every rank's 128-byte exchange-area descriptor and import the whole set on this rank, so that the
+    all-reduces of the decode step run as the library's own peer-memory kernel instead of NCCL calls."""
+    import torch
+    mine = torch.frombuffer(bytearray(ctx.export_peer()), dtype=torch.uint8).to(device or "cpu")
+    world = dist.get_world_size()
+    parts = [torch.zeros(128, dtype=torch.uint8, device=device or "cpu") for _ in range(world)]
+    dist.all_gather(parts, mine)
+    ctx.import_peers(b"".join(bytes(p.cpu().numpy().tobytes()) for p in parts))

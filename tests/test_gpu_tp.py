@@ -12,7 +12,7 @@ torch = pytest.importorskip("torch")
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank: int, world: int, port: int, key: str, out_q):
+def _worker(rank: int, world: int, port: int, key: str, push: bool, out_q):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
 
@@ -25,6 +25,8 @@ def _worker(rank: int, world: int, port: int, key: str, out_q):
         uid = tp.share_unique_id(dist, rank, CudaContext.tp_unique_id)
         cfg = synth.get_config(key, gain_std=0.1)
         factory = LlamaModelFactory(rank, rank, world, uid)
+        if push:
+            tp.connect_peers(dist, factory.ctx)  # all-reduces through peer memory instead of NCCL
         model = LlamaModel(factory.ctx, synth.metadata(cfg), synthetic_tensors(cfg, 0), 48, kv_dtype="f32")
         ref = O.OracleModel(cfg, ctx=48).load_synthetic(0)
         toks = synth.prompt_ids(cfg, 12, 0)
@@ -52,15 +54,16 @@ def _worker(rank: int, world: int, port: int, key: str, out_q):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("push", [False, True], ids=["nccl", "peer-memory"])
 @pytest.mark.parametrize("world,key", [(2, "c0"), (2, "s1"), (4, "s1")])
-def test_tensor_parallel_matches_oracle(world, key):
+def test_tensor_parallel_matches_oracle(world, key, push):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29700 + (os.getpid() + world * 7) % 2000
-    procs = [ctx.Process(target=_worker, args=(r, world, port, key, q)) for r in range(world)]
+    port = 29700 + (os.getpid() + world * 7 + (3 if push else 0)) % 2000
+    procs = [ctx.Process(target=_worker, args=(r, world, port, key, push, q)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=300) for _ in procs]
