@@ -297,15 +297,16 @@ def main():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="c1", choices=["c0", "c1", "c2", "c3", "s1"])
+    ap.add_argument("--config", default="c1", choices=["c0", "c1", "c2", "c3", "c4", "s1"])
     ap.add_argument("--kv-dtype", default="f16", choices=["f16", "f32", "auto"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--nccl-allreduce", action="store_true", help="N > 1: use NCCL all-reduces instead of the peer-memory kernel")
-    ap.add_argument("--prompt-len", type=int, default=128, help="shorter prompts are for profiler captures only")
+    ap.add_argument("--prompt-len", type=int, default=0,
+                    help="0 = the configuration's own prompt length (c1 128, c2 2048, c3 1024, c4 32768)")
     args = ap.parse_args()
     global PROMPT_LEN
-    PROMPT_LEN = args.prompt_len
+    PROMPT_LEN = args.prompt_len or {"c2": 2048, "c3": 1024, "c4": 32768}.get(args.config, 128)
     from nfai_b200 import synth
     cfg = synth.get_config(args.config)
     if args.impl == "reference":
