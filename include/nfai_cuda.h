@@ -273,6 +273,13 @@ size_t nfai_op_attn_scratch_bytes(uint32_t qH, uint32_t kvH, uint32_t d, uint32_
 int nfai_op_attn_decode_static(nfai_ctx* ctx, const float* q, const void* kcache, const void* vcache, int kv_dtype,
                                uint32_t seq, uint32_t qH, uint32_t kvH, uint32_t d, float* out);
 
+/* C[M][N] (float32) = A[M][K] * W[N][K]^T with A and W float16 (K contiguous, K % 8 == 0, 16-byte aligned): the
+ * tensor-core GEMM (TMA-fed tcgen05, accumulators in tensor memory) that the batched prompt path uses for the
+ * Q/K/V, O, gate/up and down projections. All pointers are device pointers.
+ * replaces: MatrixMultiplyShader with inputRows > 1 (NFAI.Vulkan.Shaders/MatrixMultiplyShader.cs:266-288), which
+ *           the reference never dispatches with more than one row. */
+int nfai_op_gemm_f16(nfai_ctx* ctx, const void* A, const void* W, uint32_t M, uint32_t N, uint32_t K, float* C);
+
 /* logits = W * RMSNorm(x) (W[V][H]) and the lowest index of their maximum into *argmax_out (device).
  * replaces: output RMSNorm + LM-head MatrixMultiplyShader (LlamaModel.cs:58-67,160-163) and
  *           SamplingUtils.ArgMax (SamplingUtils.cs:55-56). */

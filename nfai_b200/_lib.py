@@ -77,6 +77,7 @@ SIGNATURES = {
     "nfai_op_attn_decode": (_i, [_vp, _vp, _vp, _vp, _i, _u32, _u32, _u32, _u32, _vp, _vp, _sz]),
     "nfai_op_attn_scratch_bytes": (_sz, [_u32, _u32, _u32, _u32]),
     "nfai_op_attn_decode_static": (_i, [_vp, _vp, _vp, _vp, _i, _u32, _u32, _u32, _u32, _vp]),
+    "nfai_op_gemm_f16": (_i, [_vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "nfai_op_lm_head": (_i, [_vp, _vp, _i, _vp, _vp, _f, _u32, _u32, _vp, _vp]),
 }
 

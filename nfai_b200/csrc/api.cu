@@ -15,6 +15,7 @@
 
 #include "../../include/nfai_cuda.h"
 #include "kernels.h"
+#include "gemm_tc.h"
 #include "megastep.h"
 #include "tp.h"
 
@@ -41,6 +42,7 @@ struct nfai_ctx {
   cudaEvent_t stage_ev[kStageSlots] = {nullptr, nullptr};
   int stage_next = 0;
   uint32_t* pin_small = nullptr;  // pinned scratch for tokens / state read-back (256 bytes)
+  uint32_t* dev_err = nullptr;    // device word for error bits of kernels that run outside a model step
   TpComm* tp = nullptr;
   bool pdl = true;
   bool use_graph = true;
@@ -635,6 +637,8 @@ static int ctx_create_common(int device, int rank, int world, const void* uid, s
     CUB(cudaEventCreateWithFlags(&c->stage_ev[i], cudaEventDisableTiming));
   }
   CUB(cudaHostAlloc((void**)&c->pin_small, 256, cudaHostAllocDefault));
+  CUB(cudaMalloc((void**)&c->dev_err, 256));
+  CUB(cudaMemset(c->dev_err, 0, 256));
   memset(c->pin_small, 0, 256);
 #undef CUB
   if (world > 1) {
@@ -684,6 +688,7 @@ int nfai_ctx_destroy(nfai_ctx* c) {
     if (c->stage_ev[i]) cudaEventDestroy(c->stage_ev[i]);
   }
   if (c->pin_small) cudaFreeHost(c->pin_small);
+  if (c->dev_err) cudaFree(c->dev_err);
   if (c->ev0) cudaEventDestroy(c->ev0);
   if (c->ev1) cudaEventDestroy(c->ev1);
   if (c->stream) cudaStreamDestroy(c->stream);
@@ -1424,6 +1429,24 @@ int nfai_op_attn_decode(nfai_ctx* c, const float* q, const void* kcache, const v
   a.tickets = (uint32_t*)((char*)scratch + tick_off);
   CU(c, cudaMemsetAsync(a.tickets, 0, (size_t)kvH * attn_head_groups(qH, kvH) * 4, c->stream));
   return op_end(c, launch_attn_decode(c->stream, kv_dtype, a, false));
+}
+
+int nfai_op_gemm_f16(nfai_ctx* c, const void* A, const void* W, uint32_t M, uint32_t N, uint32_t K, float* C) {
+  int rc = op_begin(c);
+  if (rc) return rc;
+  if (!A || !W || !C || !M || !N || !K) return fail(c, NFAI_ERR_ARG, "bad argument");
+  if (K % 8) return fail(c, NFAI_ERR_ARG, "K must be a multiple of 8");
+  if (((uintptr_t)A | (uintptr_t)W) & 15) return fail(c, NFAI_ERR_ARG, "A and W must be 16-byte aligned");
+  CU(c, cudaMemsetAsync(c->dev_err, 0, 4, c->stream));
+  GemmEpilogue ep;
+  ep.kind = GEMM_EPI_STORE;
+  ep.out_f32 = C;
+  rc = op_end(c, launch_gemm_tc(c->stream, (const __half*)A, (const __half*)W, M, N, K, ep, c->dev_err));
+  if (rc) return rc;
+  uint32_t err = 0;
+  CU(c, cudaMemcpy(&err, c->dev_err, 4, cudaMemcpyDeviceToHost));
+  if (err) return fail(c, NFAI_ERR_TIMEOUT, "a bounded wait inside the tensor-core GEMM gave up");
+  return NFAI_OK;
 }
 
 int nfai_op_lm_head(nfai_ctx* c, const void* W, int dtype, const float* x, const float* gain, float eps, uint32_t H, uint32_t V,

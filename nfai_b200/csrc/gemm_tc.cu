@@ -1,0 +1,379 @@
+// Prompt-ingestion GEMM on the 5th-generation tensor cores: C[M][N] = A[M][K] * W[N][K]^T, A and W float16 with K
+// contiguous, float32 accumulation in tensor memory. M = prompt tokens of a chunk, N = output features.
+//
+// The reference has no batched prompt path (it pushes prompt tokens through the single-token shaders one by one:
+// NFAI.Models.Llama3/LlamaModel.cs:103-126); results must equal that token-by-token evaluation within the FP16
+// tolerance, so the fused epilogues below are the same ones the decode GEMVs use (RoPE + cache write, SiLU*up,
+// residual add) applied row by row.
+//
+// Shape of one CTA (192 threads, one 128 x BN output tile):
+//   warp 0      producer: one lane issues TMA tile loads (A 128x64, W BNx64 halves, 128-byte swizzle) into a ring of
+//               shared-memory stages, completion counted on the stage's "full" mbarrier;
+//   warp 1      MMA: allocates BN tensor-memory columns; one lane waits for a full stage, issues four
+//               tcgen05.mma (K = 16 each) from shared-memory descriptors, and commits to the stage's "empty"
+//               mbarrier so that the producer may refill it; after the last stage it commits to "accumulator ready";
+//   warps 2-5   epilogue: each reads its 32 accumulator rows with tcgen05.ld and applies the epilogue.
+// No cluster-wide delivery is used anywhere. Every mbarrier wait is bounded (one second): on a time-out the role
+// records an error bit and leaves; the tensor memory is released on every path.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_tc.h"
+
+namespace nfai {
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;  // halves per stage row = 128 bytes = one swizzle span
+constexpr int kGemmThreads = 192;
+constexpr unsigned long long kGemmWaitNs = 1000000000ull;
+
+__device__ __forceinline__ unsigned long long g_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait; false after one second.
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
+  if (bar_try(bar, parity)) return true;
+  const unsigned long long t0 = g_ns();
+  uint32_t polls = 0;
+  while (!bar_try(bar, parity)) {
+    if ((++polls & 63u) == 0 && g_ns() - t0 > kGemmWaitNs) return false;
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);   // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                     // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;           // stride byte offset: next 8-row group
+  d |= (uint64_t)1 << 46;                     // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                     // layout: 128-byte swizzle
+  return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// ---- epilogues: 32 consecutive output columns [n0, n0+32) of row m ---------------------------------------------
+__device__ __forceinline__ void epilogue_cols(const GemmEpilogue& ep, uint32_t m, uint32_t n0, uint32_t N, const float (&v)[32]) {
+  switch (ep.kind) {
+    case GEMM_EPI_STORE: {
+      float* out = ep.out_f32 + (size_t)m * N;
+      const float* res = ep.resid ? ep.resid + (size_t)m * N : nullptr;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (n0 + i < N) out[n0 + i] = res ? res[n0 + i] + v[i] : v[i];
+      break;
+    }
+    case GEMM_EPI_SILU_MUL: {  // columns (2j, 2j+1) = (gate_j, up_j); h_j = up * silu(gate), stored as float16
+      __half* out = ep.out_f16 + (size_t)m * (N / 2);
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        if (n0 + i + 1 < N) {
+          const float gate = v[i], up = v[i + 1];
+          const float sig = __fdiv_rn(1.0f, 1.0f + expf(-gate));
+          out[(n0 + i) >> 1] = __float2half_rn(__fmul_rn(up, __fmul_rn(gate, sig)));
+        }
+      }
+      break;
+    }
+    case GEMM_EPI_QKV_ROPE: {  // columns [Q | K | V]; RoPE on adjacent pairs at position pos0 + m
+      const uint32_t pos = ep.pos0 + m;
+      float* qrow = ep.out_f32 + (size_t)m * ep.qDim;
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const uint32_t n = n0 + i;
+        if (n >= N) continue;
+        float a = v[i], b = v[i + 1];
+        if (n < ep.qDim + ep.kvDim) {
+          const uint32_t local = n < ep.qDim ? n : n - ep.qDim;
+          const uint32_t e = local % ep.d;
+          if (e < ep.ropeDim) {
+            const float2 cs = ep.rope_cs[(size_t)pos * (ep.ropeDim / 2) + (e >> 1)];
+            const float v1 = __fsub_rn(__fmul_rn(cs.x, a), __fmul_rn(cs.y, b));
+            const float v2 = __fadd_rn(__fmul_rn(cs.y, a), __fmul_rn(cs.x, b));
+            a = v1;
+            b = v2;
+          }
+          if (n < ep.qDim) {
+            qrow[n] = a;
+            qrow[n + 1] = b;
+          } else if (ep.kv_f16) {
+            __half* kc = reinterpret_cast<__half*>(ep.kcache) + (size_t)pos * ep.kvDim + local;
+            kc[0] = __float2half_rn(a);
+            kc[1] = __float2half_rn(b);
+          } else {
+            float* kc = reinterpret_cast<float*>(ep.kcache) + (size_t)pos * ep.kvDim + local;
+            kc[0] = a;
+            kc[1] = b;
+          }
+        } else {
+          const uint32_t local = n - ep.qDim - ep.kvDim;
+          if (ep.kv_f16) {
+            __half* vc = reinterpret_cast<__half*>(ep.vcache) + (size_t)pos * ep.kvDim + local;
+            vc[0] = __float2half_rn(a);
+            vc[1] = __float2half_rn(b);
+          } else {
+            float* vc = reinterpret_cast<float*>(ep.vcache) + (size_t)pos * ep.kvDim + local;
+            vc[0] = a;
+            vc[1] = b;
+          }
+        }
+      }
+      break;
+    }
+  }
+}
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr uint32_t kABytes = kBM * kBK * 2;
+  static constexpr uint32_t kBBytes = BN * kBK * 2;
+  static constexpr uint32_t kStage = kABytes + kBBytes;
+  static constexpr uint32_t kBarOff = STAGES * kStage;
+  static constexpr uint32_t kTotal = kBarOff + 256 + 1024;  // barriers + slack for the 1024-byte alignment
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+                                                               const __grid_constant__ CUtensorMap mapW, uint32_t M,
+                                                               uint32_t N, uint32_t K, const GemmEpilogue ep,
+                                                               uint32_t* err) {
+  using SM = GemmSmem<BN, STAGES>;
+  extern __shared__ unsigned char gsm_raw[];
+  unsigned char* gsm = reinterpret_cast<unsigned char*>(((uintptr_t)gsm_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(gsm + SM::kBarOff);
+  // bars[0..STAGES) full, [STAGES..2*STAGES) empty, [2*STAGES] accumulator ready; then the TMEM base address word
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+  const uint32_t full0 = s_u32(bars), empty0 = s_u32(bars + STAGES), accbar = s_u32(bars + 2 * STAGES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
+  const uint32_t KT = (K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      bar_init(full0 + 8 * s, 1);
+      bar_init(empty0 + 8 * s, 1);
+    }
+    bar_init(accbar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // the MMA warp owns the tensor-memory allocation
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_u32(tmem_slot)), "r"((uint32_t)BN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (uint32_t kt = 0; kt < KT; ++kt) {
+        const uint32_t s = kt % STAGES;
+        if (kt >= (uint32_t)STAGES) {
+          if (!bar_wait(empty0 + 8 * s, ((kt / STAGES) - 1) & 1)) { ok = false; break; }
+        }
+        const uint32_t a_dst = s_u32(gsm + s * SM::kStage), b_dst = a_dst + SM::kABytes;
+        bar_expect_tx(full0 + 8 * s, SM::kABytes + SM::kBBytes);
+        tma_load_2d(a_dst, &mapA, (int)(kt * kBK), (int)m0, full0 + 8 * s);
+        tma_load_2d(b_dst, &mapW, (int)(kt * kBK), (int)n0, full0 + 8 * s);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // instruction descriptor: D float32, A and B float16, both K-major, N = BN, M = 128
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      for (uint32_t kt = 0; kt < KT; ++kt) {
+        const uint32_t s = kt % STAGES;
+        if (!bar_wait(full0 + 8 * s, (kt / STAGES) & 1)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_s = s_u32(gsm + s * SM::kStage), b_s = a_s + SM::kABytes;
+#pragma unroll
+        for (int k = 0; k < kBK / 16; ++k) {
+          umma_f16(tmem_base, smem_desc_sw128(a_s + k * 32), smem_desc_sw128(b_s + k * 32), idesc, (kt | (uint32_t)k) != 0);
+        }
+        umma_commit(empty0 + 8 * s);  // arrives when the MMAs above have finished reading the stage
+      }
+      if (ok) umma_commit(accbar);
+    }
+  } else {
+    // epilogue warps 2..5: warp w may touch tensor-memory lanes 32*(w%4) .. +31
+    const uint32_t lane_grp = (uint32_t)(warp & 3);
+    ok = bar_wait(accbar, 0);
+    ok = __all_sync(0xffffffffu, ok);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const uint32_t m = m0 + lane_grp * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        float v[32];
+        tmem_ld32(tmem_base + ((lane_grp * 32u) << 16) + (uint32_t)c * 32u, v);
+        if (m < M && n0 + c * 32 < N) epilogue_cols(ep, m, n0 + c * 32, N, v);
+      }
+    }
+  }
+  if (!ok && lane == 0 && err) atomicOr(err, 4u);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+  }
+}
+
+// ---- small producers of the float16 A operands ----------------------------------------------------------------
+__global__ void __launch_bounds__(256) rmsnorm_to_half_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+                                                              float eps, uint32_t H, __half* __restrict__ out) {
+  __shared__ float red[8];
+  const float* xr = x + (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (uint32_t i = threadIdx.x; i < H; i += 256) ss = fmaf(xr[i], xr[i], ss);
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) tot += red[w];
+  const float rms = sqrtf(__fdiv_rn(tot, (float)H) + eps);
+  __half* o = out + (size_t)blockIdx.x * H;
+  for (uint32_t i = threadIdx.x; i < H; i += 256) o[i] = __float2half_rn(__fmul_rn(__fdiv_rn(xr[i], rms), gain[i]));
+}
+
+__global__ void embed_rows_kernel(const __half* __restrict__ E, const uint32_t* __restrict__ tokens, uint32_t H,
+                                  float* __restrict__ x) {
+  const __half* row = E + (size_t)tokens[blockIdx.x] * H;
+  float* o = x + (size_t)blockIdx.x * H;
+  for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) o[i] = __half2float(row[i]);
+}
+
+__global__ void float_to_half_kernel(const float* __restrict__ in, __half* __restrict__ out, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = __float2half_rn(in[i]);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p) return nullptr;
+  fn = (EncodeTiledFn)p;
+  return fn;
+}
+
+// [rows][K] float16, K contiguous; box = 64 halves x box_rows rows, 128-byte swizzle, zero fill outside.
+bool make_map(CUtensorMap* map, const __half* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {K, rows};
+  cuuint64_t strides[1] = {K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES>
+cudaError_t launch_bn(cudaStream_t s, const __half* A, const __half* W, uint32_t M, uint32_t N, uint32_t K,
+                      const GemmEpilogue& ep, uint32_t* err) {
+  CUtensorMap mapA, mapW;
+  if (!make_map(&mapA, A, M, K, kBM) || !make_map(&mapW, W, N, K, BN)) return cudaErrorInvalidValue;
+  auto kern = gemm_tc_kernel<BN, STAGES>;
+  const size_t smem = GemmSmem<BN, STAGES>::kTotal;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  dim3 grid((N + BN - 1) / BN, (M + kBM - 1) / kBM);
+  kern<<<grid, kGemmThreads, smem, s>>>(mapA, mapW, M, N, K, ep, err);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_gemm_tc(cudaStream_t s, const __half* A, const __half* W, uint32_t M, uint32_t N, uint32_t K,
+                           const GemmEpilogue& ep, uint32_t* err) {
+  if (!A || !W || !M || !N || !K || (K & 7u) || (((uintptr_t)A | (uintptr_t)W) & 15)) return cudaErrorInvalidValue;
+  if ((ep.kind == GEMM_EPI_SILU_MUL || ep.kind == GEMM_EPI_QKV_ROPE) && (N & 1u)) return cudaErrorInvalidValue;
+  // enough CTAs to pull weights with every SM when the chunk is a single row of tiles
+  const uint32_t mtiles = (M + kBM - 1) / kBM;
+  if (mtiles * ((N + 127) / 128) >= 120) return launch_bn<128, 4>(s, A, W, M, N, K, ep, err);
+  if (mtiles * ((N + 63) / 64) >= 120) return launch_bn<64, 6>(s, A, W, M, N, K, ep, err);
+  return launch_bn<32, 8>(s, A, W, M, N, K, ep, err);
+}
+
+cudaError_t launch_rmsnorm_to_half(cudaStream_t s, const float* x, const float* gain, float eps, uint32_t M, uint32_t H,
+                                   __half* out) {
+  rmsnorm_to_half_kernel<<<M, 256, 0, s>>>(x, gain, eps, H, out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_embed_rows(cudaStream_t s, const __half* E, const uint32_t* tokens, uint32_t M, uint32_t H, float* x) {
+  embed_rows_kernel<<<M, 256, 0, s>>>(E, tokens, H, x);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_float_to_half(cudaStream_t s, const float* in, __half* out, size_t n) {
+  size_t want = (n + 255) / 256;
+  float_to_half_kernel<<<(unsigned)(want < 2368 ? want : 2368), 256, 0, s>>>(in, out, n);
+  return cudaGetLastError();
+}
+
+}  // namespace nfai
