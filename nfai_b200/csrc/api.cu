@@ -150,6 +150,16 @@ struct nfai_model {
   size_t fused_smem = 0;
   uint32_t fused_S_max = 1;
   unsigned long long* trace = nullptr;  // device buffer of phase time stamps (only with NFAI_TRACE=1)
+  // batched prompt path (float16 weights, one GPU): chunk workspace
+  bool prefill_gemm = false;
+  uint32_t pf_chunk = 0;
+  float* pfX0 = nullptr;      // [chunk][H] residual stream
+  float* pfX1 = nullptr;      // [chunk][H]
+  __half* pfA = nullptr;      // [chunk][max(H, qDim)] normalised activations
+  float* pfQ = nullptr;       // [chunk][qDim] rotated queries
+  __half* pfAO = nullptr;     // [chunk][qDim] attention output
+  __half* pfH = nullptr;      // [chunk][F] SiLU(gate)*up
+  uint32_t* pfTok = nullptr;  // [chunk]
   // L2 look-ahead: how far beyond the weights a kernel consumes the step's weight sequence is requested
   uint64_t pf_look = 0, pf_extra = 0;
   int pf_mode = 1;
@@ -898,6 +908,18 @@ int nfai_model_finalize(nfai_model* m) {
   const size_t o_hi = take((size_t)hp.ctx * 4);
   const size_t o_pr = take((size_t)hp.ctx * 4);
   const size_t o_tp = take((size_t)hp.H * 4);
+  // batched prompt workspace
+  const bool want_pf = hp.weight_dtype == NFAI_F16 && c->world == 1 && env_int("NFAI_PREFILL_GEMM", 1) != 0 &&
+                       hp.H % 8 == 0 && m->qDimL % 8 == 0 && m->Fl % 8 == 0;
+  const uint32_t pfc = want_pf ? (hp.ctx < 256 ? hp.ctx : 256u) : 0;
+  const uint32_t amax = hp.H > m->qDimL ? hp.H : m->qDimL;
+  const size_t o_px0 = take((size_t)pfc * hp.H * 4);
+  const size_t o_px1 = take((size_t)pfc * hp.H * 4);
+  const size_t o_pa = take((size_t)pfc * amax * 2);
+  const size_t o_pq = take((size_t)pfc * m->qDimL * 4);
+  const size_t o_pao = take((size_t)pfc * m->qDimL * 2);
+  const size_t o_ph = take((size_t)pfc * m->Fl * 2);
+  const size_t o_pt = take((size_t)pfc * 4 + 4);
   const size_t o_sw = take(64);
   const size_t o_df = take(sizeof(StepDesc));
   const size_t o_dn = take(sizeof(StepDesc));
@@ -922,6 +944,15 @@ int nfai_model_finalize(nfai_model* m) {
   m->history = (uint32_t*)(m->rarena + o_hi);
   m->prompt = (uint32_t*)(m->rarena + o_pr);
   m->tp_buf = (float*)(m->rarena + o_tp);
+  m->prefill_gemm = want_pf && pfc > 0;
+  m->pf_chunk = pfc;
+  m->pfX0 = (float*)(m->rarena + o_px0);
+  m->pfX1 = (float*)(m->rarena + o_px1);
+  m->pfA = (__half*)(m->rarena + o_pa);
+  m->pfQ = (float*)(m->rarena + o_pq);
+  m->pfAO = (__half*)(m->rarena + o_pao);
+  m->pfH = (__half*)(m->rarena + o_ph);
+  m->pfTok = (uint32_t*)(m->rarena + o_pt);
   m->sync_words = (uint32_t*)(m->rarena + o_sw);
   m->desc_full = (StepDesc*)(m->rarena + o_df);
   m->desc_nohead = (StepDesc*)(m->rarena + o_dn);
@@ -1036,6 +1067,63 @@ int nfai_decode(nfai_model* m, uint32_t token, float* logits, uint32_t* argmax) 
   return fetch_outputs(m, logits, argmax);
 }
 
+// Batched prompt ingestion (float16 weights): every projection of a chunk of tokens is one tensor-core GEMM, the
+// causal attention one kernel per layer; K and V rows land in the cache exactly where the token-by-token path puts
+// them. The LM head runs for the last token only (the reference evaluates and discards it for every prompt token:
+// NFAI.Models.Llama3/LlamaModel.cs:103-126).
+static int prefill_batched(nfai_model* m, const uint32_t* tokens, int n) {
+  nfai_ctx* c = m->ctx;
+  const nfai_hparams& hp = m->hp;
+  cudaStream_t s = c->stream;
+  const int kvdt = hp.kv_dtype;
+  const size_t kvs = dtype_size(kvdt);
+  uint32_t* err = &m->state->err;
+  uint32_t pos0 = m->pos;
+  int done = 0;
+  while (done < n) {
+    const uint32_t T = (uint32_t)(n - done) < m->pf_chunk ? (uint32_t)(n - done) : m->pf_chunk;
+    const bool last_chunk = done + (int)T == n;
+    CU(c, cudaMemcpyAsync(m->pfTok, tokens + done, (size_t)T * 4, cudaMemcpyHostToDevice, s));
+    CU(c, launch_embed_rows(s, (const __half*)m->embd.ptr, m->pfTok, T, hp.H, m->pfX0));
+    for (uint32_t l = 0; l < hp.L; ++l) {
+      const LayerW& L = m->layers[l];
+      char* kcl = (char*)m->kc + (size_t)l * kv_layer_elems(m) * kvs;
+      char* vcl = (char*)m->vc + (size_t)l * kv_layer_elems(m) * kvs;
+      CU(c, launch_rmsnorm_to_half(s, m->pfX0, L.attn_norm.ptr, hp.eps, T, hp.H, m->pfA));
+      GemmEpilogue eq;
+      eq.kind = GEMM_EPI_QKV_ROPE;
+      eq.out_f32 = m->pfQ; eq.kcache = kcl; eq.vcache = vcl; eq.kv_f16 = kvdt == NFAI_F16;
+      eq.qDim = m->qDimL; eq.kvDim = m->kvDimL; eq.d = hp.d; eq.ropeDim = hp.ropeDim; eq.pos0 = pos0; eq.rope_cs = m->rope_cs;
+      CU(c, launch_gemm_tc(s, m->pfA, (const __half*)L.qkv.ptr, T, m->qDimL + 2 * m->kvDimL, hp.H, eq, err));
+      AttnParams a;
+      a.q = m->pfQ; a.kcache = kcl; a.vcache = vcl; a.qH = m->qHl; a.kvH = m->kvHl; a.d = hp.d;
+      a.seq_imm = pos0 + 1; a.out_half = m->pfAO;
+      CU(c, launch_attn_prefill(s, kvdt, a, T));
+      GemmEpilogue eo;
+      eo.kind = GEMM_EPI_STORE; eo.out_f32 = m->pfX1; eo.resid = m->pfX0;
+      CU(c, launch_gemm_tc(s, m->pfAO, (const __half*)L.o.ptr, T, hp.H, m->qDimL, eo, err));
+      CU(c, launch_rmsnorm_to_half(s, m->pfX1, L.ffn_norm.ptr, hp.eps, T, hp.H, m->pfA));
+      GemmEpilogue eg;
+      eg.kind = GEMM_EPI_SILU_MUL; eg.out_f16 = m->pfH;
+      CU(c, launch_gemm_tc(s, m->pfA, (const __half*)L.gateup.ptr, T, 2 * m->Fl, hp.H, eg, err));
+      GemmEpilogue ed;
+      ed.kind = GEMM_EPI_STORE; ed.out_f32 = m->pfX0; ed.resid = m->pfX1;
+      CU(c, launch_gemm_tc(s, m->pfH, (const __half*)L.down.ptr, T, hp.H, m->Fl, ed, err));
+      if (last_chunk)  // the last token's residual stream after this block, where the taps and the LM head expect it
+        CU(c, cudaMemcpyAsync(x_in(m, l + 1), m->pfX0 + (size_t)(T - 1) * hp.H, (size_t)hp.H * 4, cudaMemcpyDeviceToDevice, s));
+    }
+    pos0 += T;
+    done += (int)T;
+  }
+  // LM head + arg-max for the last token; the finishing kernel advances the position by one
+  int rc = set_state_word(m, offsetof(StepState, pos), pos0 - 1, 3);
+  if (rc) return rc;
+  CU(c, launch_gemv(s, hp.weight_dtype, kvdt, EPI_LOGITS, head_params(m), m->tune_head, false));
+  CU(c, launch_argmax_final(s, m->part_val, m->part_idx, m->nparts, m->state, nullptr, m->history, hp.ctx, PrefetchPlan(),
+                            nullptr, 0, false));
+  return NFAI_OK;
+}
+
 int nfai_prefill(nfai_model* m, const uint32_t* tokens, int n, float* logits_last, uint32_t* argmax_last) {
   int rc = ready(m);
   if (rc) return rc;
@@ -1045,6 +1133,11 @@ int nfai_prefill(nfai_model* m, const uint32_t* tokens, int n, float* logits_las
     return fail(c, NFAI_ERR_CONTEXT_FULL, "prompt of %d tokens at position %u exceeds the KV-cache capacity %u", n, m->pos, m->hp.ctx);
   for (int i = 0; i < n; ++i)
     if (tokens[i] >= m->hp.V) return fail(c, NFAI_ERR_ARG, "token id %u out of range (V = %u)", tokens[i], m->hp.V);
+  if (m->prefill_gemm && n >= 8) {
+    if ((rc = prefill_batched(m, tokens, n))) return rc;
+    m->pos += (uint32_t)n;
+    return fetch_outputs(m, logits_last, argmax_last);
+  }
   if (n > 1) {
     CU(c, cudaMemcpyAsync(m->prompt, tokens, (size_t)(n - 1) * 4, cudaMemcpyHostToDevice, c->stream));
     if ((rc = set_state_word(m, offsetof(StepState, prompt_idx), 0, 1))) return rc;

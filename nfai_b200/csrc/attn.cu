@@ -42,6 +42,29 @@ __global__ void __launch_bounds__(kAT, 1) attn_decode_kernel(const AttnParams p)
   attn_core<KVT, D, kAW, false, GH, (GH == 1 ? 2 * KV8<KVT>::kUnroll : 0)>(p, blockIdx.x, blockIdx.y, seq, p.min_chunk);
 }
 
+// Prompt path: blockIdx.y is the token of the chunk; its sequence is one longer than the previous token's.
+template <typename KVT, int D>
+__global__ void __launch_bounds__(kAT, 1) attn_prefill_kernel(const AttnParams p) {
+  const uint32_t t = blockIdx.y;
+  AttnParams pp = p;
+  pp.q = p.q + (size_t)t * p.qH * D;
+  pp.out_half = p.out_half + (size_t)t * p.qH * D;
+  pp.S_max = 1;
+  attn_core<KVT, D, kAW, false, (int)kAttnHeadsPerCta>(pp, blockIdx.x, 0, p.seq_imm + t, 1u << 30);
+}
+
+template <typename KVT>
+cudaError_t launch_p(cudaStream_t s, const AttnParams& p, uint32_t T) {
+  dim3 grid(p.kvH * attn_head_groups(p.qH, p.kvH), T);
+  switch (p.d) {
+    case 32: attn_prefill_kernel<KVT, 32><<<grid, kAT, 0, s>>>(p); break;
+    case 64: attn_prefill_kernel<KVT, 64><<<grid, kAT, 0, s>>>(p); break;
+    case 128: attn_prefill_kernel<KVT, 128><<<grid, kAT, 0, s>>>(p); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
 template <typename KVT>
 cudaError_t launch_d(cudaStream_t s, const AttnParams& p, bool pdl) {
   const uint32_t hgroups = attn_head_groups(p.qH, p.kvH, p.heads_per_cta);
@@ -98,6 +121,11 @@ uint32_t attn_splits(uint32_t qH, uint32_t kvH, uint32_t max_seq, uint32_t heads
 }
 
 size_t attn_part_floats(uint32_t qH, uint32_t d, uint32_t S_max) { return (size_t)qH * S_max * (d + 2); }
+
+cudaError_t launch_attn_prefill(cudaStream_t s, int kvdtype, const AttnParams& p, uint32_t T) {
+  if (p.qH == 0 || p.kvH == 0 || p.qH % p.kvH != 0 || !p.out_half || !p.seq_imm || !T || T > 65535) return cudaErrorInvalidValue;
+  return kvdtype == 1 ? launch_p<__half>(s, p, T) : launch_p<float>(s, p, T);
+}
 
 cudaError_t launch_attn_decode(cudaStream_t s, int kvdtype, const AttnParams& p, bool pdl) {
   if (p.qH == 0 || p.kvH == 0 || p.qH % p.kvH != 0 || p.S_max == 0) return cudaErrorInvalidValue;

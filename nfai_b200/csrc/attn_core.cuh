@@ -213,8 +213,13 @@ __device__ __forceinline__ void attn_core(const AttnParams& p, const uint32_t bx
     float o = 0.f;
 #pragma unroll
     for (int w = 0; w < kAW; ++w) o = fmaf(wpart[w][j][i], fin_scale[w][j], o);
-    if (S_eff == 1)
-      p.out[(h0 + j) * D + i] = o * (1.0f / fin_ML[j][1]);
+    if (S_eff == 1) {
+      const float r = o * (1.0f / fin_ML[j][1]);
+      if (p.out_half)
+        p.out_half[(h0 + j) * D + i] = __float2half_rn(r);
+      else
+        p.out[(h0 + j) * D + i] = r;
+    }
     else
       p.part[((size_t)(h0 + j) * p.S_max + s) * pstride + i] = o;
   }

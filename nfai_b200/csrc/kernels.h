@@ -1,5 +1,6 @@
 // Host-side launch interface of the kernels in libnfai_cuda (internal; the public ABI is include/nfai_cuda.h).
 #pragma once
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -94,6 +95,7 @@ struct AttnParams {
   StepState* state = nullptr;  // seq = state->pos + 1 when non-null
   uint32_t seq_imm = 0;
   float* out = nullptr;        // [qH*d]
+  __half* out_half = nullptr;  // when non-null the output goes here as float16 instead (prompt path: the next GEMM's A)
   float* part = nullptr;       // [qH][S_max][d+2] split partials
   uint32_t* tickets = nullptr; // [kvH * head_groups], zero between launches
   uint32_t S_max = 1;
@@ -114,6 +116,9 @@ uint32_t attn_splits(uint32_t qH, uint32_t kvH, uint32_t max_seq, uint32_t heads
                      uint32_t min_chunk = kAttnMinChunk);
 size_t attn_part_floats(uint32_t qH, uint32_t d, uint32_t S_max);
 cudaError_t launch_attn_decode(cudaStream_t s, int kvdtype, const AttnParams& p, bool pdl);
+// Causal attention of T prompt tokens: token t (q row t of p.q, [T][qH*d]) attends to positions 0 .. p.seq_imm-1+t;
+// output rows go to p.out_half ([T][qH*d] float16). One CTA per (KV head group, token), no split.
+cudaError_t launch_attn_prefill(cudaStream_t s, int kvdtype, const AttnParams& p, uint32_t T);
 
 cudaError_t launch_embed(cudaStream_t s, int wdtype, const void* E, uint32_t H, uint32_t V, StepState* state,
                          const uint32_t* prompt, uint32_t token_imm, float* x_out, const PrefetchPlan& pf, bool pdl);
