@@ -204,11 +204,13 @@ int nfai_model_tune(nfai_model* m, int which, int mode, int rows_per_warp, int d
  * No counterpart in the reference. */
 int nfai_model_set_prefetch(nfai_model* m, uint64_t lookahead_bytes, uint64_t extra_bytes, int mode);
 
-/* Run the decode step as ONE persistent kernel (grid barriers between its phases, the next phase's weights
- * requested before each barrier) instead of 3 + 5L kernels. Same arithmetic, same results. Available on one GPU when
- * the whole grid is co-resident; enabled != 0 switches it on and captures the decode graphs again.
- * No counterpart in the reference (it submits and waits for every dispatch: ShaderWrapper.cs:208-245). */
-int nfai_model_set_fused_step(nfai_model* m, int enabled);
+/* Run the decode step as ONE persistent kernel instead of 3 + 5L kernels (grid barriers between its phases).
+ * mode 0: one kernel per operation (default); mode 1: fused, the next phase's first weights are requested into
+ * registers before each barrier; mode 2: fused, every warp streams its rows of ALL matrices of the step through a
+ * shared-memory ring fed by bulk asynchronous copies, so the weight stream continues across the barriers.
+ * Same arithmetic, same results. One GPU only; the whole grid must be co-resident. The decode graphs are
+ * captured again. No counterpart in the reference (it submits and waits for every dispatch: ShaderWrapper.cs:208-245). */
+int nfai_model_set_fused_step(nfai_model* m, int mode);
 
 /* Diagnostics of the fused step: with NFAI_TRACE=1 in the environment at nfai_model_finalize, CTA 0 records a
  * %globaltimer value (nanoseconds) at every phase end and barrier of the last step; this copies up to `capacity`

@@ -222,8 +222,9 @@ class LlamaModel:
         check(self._lib.nfai_model_set_prefetch(self.handle, int(lookahead_bytes), int(extra_bytes), mode),
               self.ctx.handle)
 
-    def set_fused_step(self, enabled: bool):
-        check(self._lib.nfai_model_set_fused_step(self.handle, 1 if enabled else 0), self.ctx.handle)
+    def set_fused_step(self, mode):
+        """0/False = one kernel per operation, 1/True = fused with register prefetch, 2 = fused with rings."""
+        check(self._lib.nfai_model_set_fused_step(self.handle, int(mode)), self.ctx.handle)
 
     def trace(self) -> np.ndarray:
         buf = np.zeros(2048, np.uint64)

@@ -141,9 +141,13 @@ struct nfai_model {
   uint32_t pos = 0;  // host mirror of state->pos
   GemvTune tune_qkv, tune_o, tune_gateup, tune_down, tune_head;
   // fused decode step (one persistent kernel per token)
-  bool use_fused = false;
+  int use_fused = 0;                // 0 = one kernel per operation, 1 = fused (register prefetch), 2 = fused (rings)
   StepDesc* desc_full = nullptr;    // device copies of the descriptors
   StepDesc* desc_nohead = nullptr;
+  StepDesc* desc_full_ring = nullptr;
+  StepDesc* desc_nohead_ring = nullptr;
+  int ring_grid = 0, ring_stages = 0;
+  size_t ring_smem = 0;
   LayerDesc* layer_desc = nullptr;
   uint32_t* sync_words = nullptr;   // [0] barrier counter, [1] abort flag
   int fused_grid = 0;
@@ -369,7 +373,11 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     // one persistent kernel; its grid barrier counter starts from zero at every launch
     e = cudaMemsetAsync(m->sync_words, 0, 8, s);
     if (e != cudaSuccess) return e;
-    e = launch_megastep(s, wdt, kvdt, hp.d, with_head ? m->desc_full : m->desc_nohead, m->fused_grid, m->fused_smem);
+    if (m->use_fused == 2)
+      e = launch_fused_ring(s, wdt, kvdt, hp.d, with_head ? m->desc_full_ring : m->desc_nohead_ring, m->ring_grid, m->ring_smem,
+                            m->ring_stages);
+    else
+      e = launch_megastep(s, wdt, kvdt, hp.d, with_head ? m->desc_full : m->desc_nohead, m->fused_grid, m->fused_smem);
     if (e != cudaSuccess) return e;
     if (launches) *launches = 1;
     return cudaSuccess;
@@ -901,7 +909,30 @@ int nfai_model_finalize(nfai_model* m) {
     if (m->fused_S_max < 1) m->fused_S_max = 1;
     if ((uint32_t)m->fused_grid < nx) m->fused_grid = 0;  // not enough CTAs for one attention item each
   }
-  const uint32_t S_alloc = m->S_max > m->fused_S_max ? m->S_max : m->fused_S_max;
+  // ring variant of the fused step: one 512-thread CTA per SM, rings as deep as shared memory allows
+  m->ring_grid = 0;
+  m->ring_stages = 0;
+  uint32_t ring_S_max = 1;
+  const uint32_t ring_heads = hp.ctx <= 4096 ? 1u : 4u;
+  const uint32_t ring_nx = ring_heads == 1 ? m->qHl : m->kvHl * ((m->qHl / m->kvHl + 3) / 4);
+  const size_t wsz = dtype_size(hp.weight_dtype);
+  if (c->world == 1 && (hp.H * wsz) % 16 == 0 && (m->qDimL * wsz) % 16 == 0 && (m->Fl * wsz) % 16 == 0) {
+    size_t rs = 0;
+    int st = 0, g = 0;
+    if (fused_ring_prepare(hp.weight_dtype, hp.kv_dtype, hp.d, hp.H, m->Fl, m->qDimL, &g, &st, &rs) == cudaSuccess && st >= 2 &&
+        (uint32_t)g >= ring_nx) {
+      m->ring_grid = g;
+      m->ring_stages = st;
+      m->ring_smem = rs;
+      uint32_t by_len = (hp.ctx + kAttnMinChunk - 1) / kAttnMinChunk;
+      uint32_t by_grid = (uint32_t)g / ring_nx;
+      ring_S_max = by_len < by_grid ? by_len : by_grid;
+      if (ring_S_max < 1) ring_S_max = 1;
+    }
+    cudaGetLastError();
+  }
+  uint32_t S_alloc = m->S_max > m->fused_S_max ? m->S_max : m->fused_S_max;
+  if (ring_S_max > S_alloc) S_alloc = ring_S_max;
   const size_t o_ap = take(attn_part_floats(m->qHl, hp.d, S_alloc) * 4);
   const size_t o_tk = take((size_t)m->qHl * 4);  // one ticket per (kv head, head group); at most one per query head
   const size_t o_st = take(sizeof(StepState));
@@ -923,6 +954,8 @@ int nfai_model_finalize(nfai_model* m) {
   const size_t o_sw = take(64);
   const size_t o_df = take(sizeof(StepDesc));
   const size_t o_dn = take(sizeof(StepDesc));
+  const size_t o_dfr = take(sizeof(StepDesc));
+  const size_t o_dnr = take(sizeof(StepDesc));
   const size_t o_ld = take(sizeof(LayerDesc) * hp.L);
   const bool want_trace = env_int("NFAI_TRACE", 0) != 0;
   const size_t o_tr = take(want_trace ? sizeof(unsigned long long) * kTraceSlots : 8);
@@ -972,7 +1005,7 @@ int nfai_model_finalize(nfai_model* m) {
     d.out_norm = m->out_norm.ptr; d.rope_cs = m->rope_cs; d.state = m->state; d.prompt = nullptr;
     d.xbuf = m->xbuf; d.q = m->q; d.attn_out = m->attn_out; d.hbuf = m->hbuf; d.logits = m->logits;
     d.part_val = m->part_val; d.part_idx = m->part_idx; d.attn_part = m->attn_part; d.tickets = m->tickets;
-    d.S_max = m->fused_S_max; d.kc = m->kc; d.vc = m->vc;
+    d.S_max = m->fused_S_max; d.attn_heads = kMegaHeadsPerCta; d.attn_min_chunk = kMegaMinChunk; d.kc = m->kc; d.vc = m->vc;
     d.kv_layer_bytes = (unsigned long long)kv_layer_elems(m) * kvs;
     d.sync_counter = m->sync_words; d.abort_flag = m->sync_words + 1;
     d.history = m->history; d.history_cap = hp.ctx; d.with_head = 1; d.layers = m->layer_desc;
@@ -982,8 +1015,19 @@ int nfai_model_finalize(nfai_model* m) {
     d.with_head = 0;
     d.prompt = m->prompt;
     CU(c, cudaMemcpy(m->desc_nohead, &d, sizeof d, cudaMemcpyHostToDevice));
+    // the ring variant has its own attention launch shape
+    m->desc_full_ring = (StepDesc*)(m->rarena + o_dfr);
+    m->desc_nohead_ring = (StepDesc*)(m->rarena + o_dnr);
+    d.S_max = ring_S_max; d.attn_heads = ring_heads; d.attn_min_chunk = kAttnMinChunk;
+    CU(c, cudaMemcpy(m->desc_nohead_ring, &d, sizeof d, cudaMemcpyHostToDevice));
+    d.with_head = 1;
+    d.prompt = nullptr;
+    CU(c, cudaMemcpy(m->desc_full_ring, &d, sizeof d, cudaMemcpyHostToDevice));
   }
-  m->use_fused = m->fused_grid > 0 && env_int("NFAI_FUSED", 0) != 0;
+  m->use_fused = env_int("NFAI_FUSED", 0);
+  if (m->use_fused == 2 && m->ring_grid <= 0) m->use_fused = 0;
+  if (m->use_fused == 1 && m->fused_grid <= 0) m->use_fused = 0;
+  if (m->use_fused < 0 || m->use_fused > 2) m->use_fused = 0;
   // RoPE table on the host, float32, as the reference builds its frequency table
   // (NFAI.Vulkan.Shaders/TransformerBlock.cs:33-38) and its shader forms theta = f[m] * float(pos)
   // (NFAI.Vulkan.Shaders/RoPEShader.cs:252-254); cos/sin from the host libm.
@@ -1316,10 +1360,11 @@ int nfai_model_set_fused_step(nfai_model* m, int enabled) {
   int rc = ready(m);
   if (rc) return rc;
   nfai_ctx* c = m->ctx;
-  if (enabled && (m->fused_grid <= 0 || c->world != 1))
-    return fail(c, NFAI_ERR_STATE, "the fused decode step is not available for this model (needs one GPU, a co-resident grid and at most 100 KB of shared memory)");
-  const bool old = m->use_fused;
-  m->use_fused = enabled != 0;
+  if (enabled < 0 || enabled > 2) return fail(c, NFAI_ERR_ARG, "mode must be 0, 1 or 2");
+  if ((enabled == 1 && m->fused_grid <= 0) || (enabled == 2 && m->ring_grid <= 0) || (enabled && c->world != 1))
+    return fail(c, NFAI_ERR_STATE, "this fused decode step is not available for this model (needs one GPU, a co-resident grid, rows that are multiples of 16 bytes and enough shared memory)");
+  const int old = m->use_fused;
+  m->use_fused = enabled;
   if (!c->use_graph) { m->launches_full = m->use_fused ? 1 : 3 + 5 * (int)m->hp.L; return NFAI_OK; }
   CU(c, cudaStreamSynchronize(c->stream));
   cudaGraphExec_t gf = nullptr, gn = nullptr;

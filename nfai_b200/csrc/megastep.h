@@ -36,6 +36,8 @@ struct StepDesc {
   float* attn_part;
   uint32_t* tickets;
   uint32_t S_max;
+  uint32_t attn_heads;      // query heads per attention CTA (ring variant: 1 or 4)
+  uint32_t attn_min_chunk;  // fewest positions per attention CTA before the range is split
   void* kc;
   void* vc;
   unsigned long long kv_layer_bytes;
@@ -57,5 +59,11 @@ size_t megastep_smem(uint32_t H, uint32_t F, uint32_t qDim);
 cudaError_t megastep_max_grid(int wdtype, int kvdtype, uint32_t d, size_t smem, int* grid_out);
 cudaError_t launch_megastep(cudaStream_t s, int wdtype, int kvdtype, uint32_t d, const StepDesc* desc_dev, int grid,
                             size_t smem);
+
+// Ring variant (fused_ring.cu): weights stream through per-warp shared-memory rings across the grid barriers.
+cudaError_t fused_ring_prepare(int wdtype, int kvdtype, uint32_t d, uint32_t H, uint32_t F, uint32_t qDim, int* grid_out,
+                               int* stages_out, size_t* smem_out);
+cudaError_t launch_fused_ring(cudaStream_t s, int wdtype, int kvdtype, uint32_t d, const StepDesc* desc_dev, int grid,
+                              size_t smem, int stages);
 
 }  // namespace nfai

@@ -17,16 +17,17 @@ def factory():
     f.Dispose()
 
 
+@pytest.mark.parametrize("mode", [1, 2], ids=["register-prefetch", "rings"])
 @pytest.mark.parametrize("key,over,kv", [("c0", {}, "f32"), ("c0p", {"gain_std": 0.1}, "f32"), ("s3", {"gain_std": 0.1}, "f16"),
                                          ("s2", {}, "f32"), ("s1", {}, "f16")])
-def test_fused_step_matches_per_kernel_path_and_oracle(factory, oracle, key, over, kv):
+def test_fused_step_matches_per_kernel_path_and_oracle(factory, oracle, key, over, kv, mode):
     cfg = synth.get_config(key, **over)
     n = 20 if key != "s1" else 8
     toks = synth.prompt_ids(cfg, n, 0)
     ref = oracle.OracleModel(cfg, ctx=64).load_synthetic(0)
     a = create_synthetic_model(cfg, 64, factory=factory, kv_dtype=kv)
     b = create_synthetic_model(cfg, 64, factory=factory, kv_dtype=kv)
-    b.set_fused_step(True)
+    b.set_fused_step(mode)
     assert b.step_launches() == 1 and a.step_launches() == 3 + 5 * cfg.L
     for i, t in enumerate(toks):
         want = ref.decode(int(t))
@@ -59,14 +60,15 @@ def test_fused_step_matches_per_kernel_path_and_oracle(factory, oracle, key, ove
     b.Dispose()
 
 
-def test_fused_step_long_context_splits(factory, oracle):
+@pytest.mark.parametrize("mode", [1, 2], ids=["register-prefetch", "rings"])
+def test_fused_step_long_context_splits(factory, oracle, mode):
     """Attention inside the fused step with several splits: seed the cache, then compare one step."""
     cfg = synth.get_config("s3", gain_std=0.1)
     ctx = 1500
     rng = np.random.default_rng(0)
     a = create_synthetic_model(cfg, ctx, factory=factory, kv_dtype="f32")
     b = create_synthetic_model(cfg, ctx, factory=factory, kv_dtype="f32")
-    b.set_fused_step(True)
+    b.set_fused_step(mode)
     npos = 1200
     for l in range(cfg.L):
         for p in range(npos):
