@@ -32,6 +32,9 @@ internal static unsafe partial class Native
     [DllImport(Lib)] internal static extern int nfai_model_tensor_chunk(IntPtr model, byte* bytes, nuint nbytes);
     [DllImport(Lib)] internal static extern int nfai_model_tensor_end(IntPtr model);
     [DllImport(Lib)] internal static extern int nfai_model_finalize(IntPtr model);
+    [DllImport(Lib, CharSet = CharSet.Ansi)] internal static extern int nfai_model_load_gguf(IntPtr ctx, string path, uint kvCacheSize, int kvDType, out IntPtr model);
+    [DllImport(Lib)] internal static extern int nfai_model_get_hparams(IntPtr model, out NfaiHParams hp);
+    [DllImport(Lib)] internal static extern int nfai_op_gemm_f16(IntPtr ctx, void* a, void* w, uint m, uint n, uint k, float* c);
     [DllImport(Lib)] internal static extern int nfai_model_destroy(IntPtr model);
     [DllImport(Lib)] internal static extern int nfai_prefill(IntPtr model, uint* tokens, int n, float* logitsLast, uint* argmaxLast);
     [DllImport(Lib)] internal static extern int nfai_decode(IntPtr model, uint token, float* logits, uint* argmax);

@@ -128,6 +128,18 @@ int nfai_model_tensor_end(nfai_model* m);
  *           ShaderWrapper.Compile on first use (NFAI.Vulkan.Shaders/ShaderWrapper.cs:55-206). */
 int nfai_model_finalize(nfai_model* m);
 
+/* Whole-file path: memory-map a GGUF file, read header, metadata and tensor directory natively, and stream the
+ * tensors of a general.architecture == "llama" model to the device in their stored type (float16 files stay
+ * float16, no widening pass on the CPU); then finalize. kv_dtype: NFAI_F32, NFAI_F16, or -1 for the weights' type.
+ * Equivalent to nfai_model_create + tensor_begin/chunk/end for every tensor + nfai_model_finalize.
+ * replaces: Parser.Parse (NFAI.GGUF/Parser.cs:22-45,130-307) + ComputeCollection.GetDataRaw
+ *           (NFAI.Core/AbstractComputeCollection.cs:36-79) + UploadDataToDeviceLocal
+ *           (NFAI.Vulkan/VulkanBufferManager.cs:105-194) for hosts that want the native loader. */
+int nfai_model_load_gguf(nfai_ctx* ctx, const char* path, uint32_t kv_cache_size, int kv_dtype, nfai_model** out);
+
+/* The model's geometry as it was created (filled by nfai_model_load_gguf from the file). */
+int nfai_model_get_hparams(const nfai_model* m, nfai_hparams* out);
+
 /* replaces: LlamaModel.Dispose (LlamaModel.cs:70-74, which throws NotImplementedException). */
 int nfai_model_destroy(nfai_model* m);
 

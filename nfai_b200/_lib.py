@@ -54,6 +54,8 @@ SIGNATURES = {
     "nfai_model_tensor_chunk": (_i, [_vp, _vp, _sz]),
     "nfai_model_tensor_end": (_i, [_vp]),
     "nfai_model_finalize": (_i, [_vp]),
+    "nfai_model_load_gguf": (_i, [_vp, C.c_char_p, _u32, _i, _pp]),
+    "nfai_model_get_hparams": (_i, [_vp, C.POINTER(HParams)]),
     "nfai_model_destroy": (_i, [_vp]),
     "nfai_prefill": (_i, [_vp, C.POINTER(_u32), _i, C.POINTER(_f), C.POINTER(_u32)]),
     "nfai_decode": (_i, [_vp, _u32, C.POINTER(_f), C.POINTER(_u32)]),

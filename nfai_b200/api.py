@@ -9,6 +9,7 @@ Every compute step runs in libnfai_cuda.so; nothing here falls back to the CPU.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
@@ -127,6 +128,25 @@ class LlamaModel:
         except Exception:
             self.Dispose()
             raise
+
+    @classmethod
+    def from_gguf_native(cls, ctx: CudaContext, path: str, context_size: int = 1024, kv_dtype: str = "auto") -> "LlamaModel":
+        """Load a GGUF file with the library's native loader (mmap, raw float16 pass-through)."""
+        self = cls.__new__(cls)
+        self.ctx = ctx
+        self._lib = _lib.load()
+        h = C.c_void_p()
+        kv = -1 if kv_dtype == "auto" else _dtype_code(kv_dtype)
+        check(self._lib.nfai_model_load_gguf(ctx.handle, path.encode(), int(context_size), kv, C.byref(h)), ctx.handle)
+        self.handle = h
+        self.hp = HParams()
+        check(self._lib.nfai_model_get_hparams(h, C.byref(self.hp)), ctx.handle)
+        self.V, self.H, self.L = self.hp.V, self.hp.H, self.hp.L
+        self.kv_dtype = "f16" if self.hp.kv_dtype == F16 else "f32"
+        self.weight_dtype = "f16" if self.hp.weight_dtype == F16 else "f32"
+        self.ModelName = os.path.basename(path)
+        self.bos_token, self.eos_token = 0, 1
+        return self
 
     # -- upload -------------------------------------------------------------------------------------------------
     def upload(self, t: ComputeCollection, widen_half: bool = False):

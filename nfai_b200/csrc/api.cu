@@ -1215,6 +1215,12 @@ int nfai_decode_greedy(nfai_model* m, uint32_t first_token, int n_steps, uint32_
   return NFAI_OK;
 }
 
+int nfai_model_get_hparams(const nfai_model* m, nfai_hparams* out) {
+  if (!m || !out) return fail(m ? m->ctx : nullptr, NFAI_ERR_ARG, "null argument");
+  *out = m->hp;
+  return NFAI_OK;
+}
+
 int nfai_position(const nfai_model* m, uint32_t* pos) {
   if (!m || !pos) return fail(m ? m->ctx : nullptr, NFAI_ERR_ARG, "null argument");
   *pos = m->pos;

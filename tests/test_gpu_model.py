@@ -197,6 +197,41 @@ def test_gguf_file_through_parser(factory, oracle, tmp_path):
     model.Dispose()
 
 
+@pytest.mark.parametrize("key", ["c0p", "s3"])
+def test_native_gguf_loader(factory, tmp_path, key):
+    """The native loader (mmap + raw pass-through) builds the same model as the tensor-by-tensor upload."""
+    from nfai_b200 import LlamaModel
+    cfg = synth.get_config(key, gain_std=0.1)
+    path = os.path.join(tmp_path, "m.gguf")
+    gguf_io.write_synthetic_gguf(cfg, path, seed=4)
+    a = LlamaModel.from_gguf_native(factory.ctx, path, 32)
+    b = create_synthetic_model(cfg, 32, seed=4, factory=factory)
+    assert (a.V, a.H, a.L) == (cfg.V, cfg.H, cfg.L) and a.weight_dtype == cfg.dtype
+    assert a.hp.qH == cfg.qH and a.hp.kvH == cfg.kvH and a.hp.F == cfg.F and a.hp.tied == (1 if cfg.tied else 0)
+    toks = synth.prompt_ids(cfg, 6, 4)
+    for t in toks:
+        la, ama = a.decode(int(t))
+        lb, amb = b.decode(int(t))
+        assert np.array_equal(la.view(np.uint32), lb.view(np.uint32)) and ama == amb
+    a.Dispose()
+    b.Dispose()
+    with pytest.raises(NfaiError) as e:
+        LlamaModel.from_gguf_native(factory.ctx, os.path.join(tmp_path, "missing.gguf"), 8)
+    assert e.value.code == _lib.ERR_ARG
+    bad = os.path.join(tmp_path, "bad.gguf")
+    with open(bad, "wb") as fh:
+        fh.write(b"NOPE" + bytes(64))
+    with pytest.raises(NfaiError) as e:
+        LlamaModel.from_gguf_native(factory.ctx, bad, 8)
+    assert e.value.code == _lib.ERR_ARG
+    trunc = os.path.join(tmp_path, "trunc.gguf")
+    with open(path, "rb") as src, open(trunc, "wb") as dst:
+        dst.write(src.read(os.path.getsize(path) // 2))
+    with pytest.raises(NfaiError) as e:
+        LlamaModel.from_gguf_native(factory.ctx, trunc, 8)
+    assert e.value.code == _lib.ERR_ARG
+
+
 def test_errors_are_statuses(factory):
     cfg = synth.get_config("c0")
     m = make(cfg, 4, factory)
