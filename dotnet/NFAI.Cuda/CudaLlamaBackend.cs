@@ -58,6 +58,14 @@ public sealed unsafe class CudaLlamaBackend : IDisposable
         return am;
     }
 
+    // SamplingUtils.TopP (SamplingUtils.cs:5-33) on the device over the logits of the last Prefill/Decode: the 513 KB
+    // logits read-back becomes a 4-byte token. The uniform draw stays on the host (Random.Shared, as today).
+    public uint SampleTopP(float temperature = 0.5f, float topP = 0.95f, int topK = 40)
+    {
+        Native.Check(Native.nfai_sample_top_p(model, temperature, topP, topK, Random.Shared.NextSingle(), out uint tok), ctx.Handle);
+        return tok;
+    }
+
     public void Reset() => Native.Check(Native.nfai_reset(model), ctx.Handle);
 
     public void Dispose()

@@ -39,6 +39,8 @@ internal static unsafe partial class Native
     [DllImport(Lib)] internal static extern int nfai_prefill(IntPtr model, uint* tokens, int n, float* logitsLast, uint* argmaxLast);
     [DllImport(Lib)] internal static extern int nfai_decode(IntPtr model, uint token, float* logits, uint* argmax);
     [DllImport(Lib)] internal static extern int nfai_decode_greedy(IntPtr model, uint firstToken, int nSteps, uint* outTokens, float* elapsedMs);
+    [DllImport(Lib)] internal static extern int nfai_sample_top_p(IntPtr model, float temperature, float topP, int topK, float u, out uint token);
+    [DllImport(Lib)] internal static extern int nfai_op_sample_top_p(IntPtr ctx, IntPtr logits, uint V, float temperature, float topP, int topK, float u, IntPtr tokenOut);
     [DllImport(Lib)] internal static extern int nfai_position(IntPtr model, out uint pos);
     [DllImport(Lib)] internal static extern int nfai_reset(IntPtr model);
     [DllImport(Lib)] internal static extern int nfai_set_position(IntPtr model, uint pos);

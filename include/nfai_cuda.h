@@ -164,6 +164,14 @@ int nfai_decode(nfai_model* m, uint32_t token, float* logits, uint32_t* argmax);
  * replaces: the decode loop of LlamaModel.RunAsync with SamplingUtils.ArgMax in place of TopP. */
 int nfai_decode_greedy(nfai_model* m, uint32_t first_token, int n_steps, uint32_t* out_tokens, float* elapsed_ms);
 
+/* Temperature / top-k / top-p sampling of the last step's logits on the device; only the token id comes back.
+ * `u` in [0, 1) is the uniform random number the draw uses (the host supplies it, e.g. Random.Shared.NextSingle()).
+ * Same arithmetic as SamplingUtils.TopP (defaults there: temperature 0.5, top_p 0.95, top_k 40); top_k <= 64.
+ * The sampled token also becomes the token a following nfai_decode_greedy-style device step would embed.
+ * replaces: lmHead.GetOutputs() (513 KB read-back) + SamplingUtils.TopP (NFAI.Models.Llama3/SamplingUtils.cs:5-33,
+ *           LlamaModel.cs:128-130,165). */
+int nfai_sample_top_p(nfai_model* m, float temperature, float top_p, int top_k, float u, uint32_t* token_out);
+
 /* Current position (number of tokens in the KV cache).
  * replaces: TransformerBlock.currentToken (TransformerBlock.cs:25,183) and
  *           MatrixMultiplyShader.currentCacheSize (NFAI.Vulkan.Shaders/MatrixMultiplyShader.cs:28). */
@@ -299,6 +307,11 @@ int nfai_op_gemm_f16(nfai_ctx* ctx, const void* A, const void* W, uint32_t M, ui
  *           SamplingUtils.ArgMax (SamplingUtils.cs:55-56). */
 int nfai_op_lm_head(nfai_ctx* ctx, const void* W, int dtype, const float* x, const float* gain, float eps, uint32_t H,
                     uint32_t V, float* logits, uint32_t* argmax_out);
+
+/* SamplingUtils.TopP alone on a device-resident logits vector (logits, token_out: device pointers).
+ * replaces: NFAI.Models.Llama3/SamplingUtils.cs:5-33. */
+int nfai_op_sample_top_p(nfai_ctx* c, const float* logits, uint32_t V, float temperature, float top_p, int top_k, float u,
+                         uint32_t* token_out);
 
 #ifdef __cplusplus
 }

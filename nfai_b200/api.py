@@ -182,6 +182,12 @@ class LlamaModel:
                                            out.ctypes.data_as(C.POINTER(C.c_uint32)), C.byref(ms)), self.ctx.handle)
         return out, ms.value
 
+    def sample_top_p(self, temperature: float = 0.5, top_p: float = 0.95, top_k: int = 40, u: float = 0.5) -> int:
+        """SamplingUtils.TopP on the device over the last step's logits; `u` is the uniform draw."""
+        tok = C.c_uint32()
+        check(self._lib.nfai_sample_top_p(self.handle, temperature, top_p, top_k, u, C.byref(tok)), self.ctx.handle)
+        return tok.value
+
     def run_tokens(self, prompt: Iterable[int], max_new: int, stop_at_eos: bool = False) -> List[int]:
         """LlamaModel.RunAsync with token ids in place of text and arg-max in place of TopP
         (LlamaModel.cs:99-174): ingest the prompt, then feed each prediction back."""

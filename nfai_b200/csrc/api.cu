@@ -136,6 +136,7 @@ struct nfai_model {
   uint32_t* prompt = nullptr;
   float* pin_logits = nullptr;  // pinned V floats
   float* tp_buf = nullptr;      // [H] partial sums exchanged between ranks
+  void* sample_scratch = nullptr;  // per-slice sums and candidates of the on-device sampler
   cudaGraphExec_t g_full = nullptr, g_nohead = nullptr;
   int launches_full = 0;
   uint32_t pos = 0;  // host mirror of state->pos
@@ -951,6 +952,7 @@ int nfai_model_finalize(nfai_model* m) {
   const size_t o_pao = take((size_t)pfc * m->qDimL * 2);
   const size_t o_ph = take((size_t)pfc * m->Fl * 2);
   const size_t o_pt = take((size_t)pfc * 4 + 4);
+  const size_t o_ss = take(sample_scratch_bytes(m->Vl, nullptr));
   const size_t o_sw = take(64);
   const size_t o_df = take(sizeof(StepDesc));
   const size_t o_dn = take(sizeof(StepDesc));
@@ -986,6 +988,7 @@ int nfai_model_finalize(nfai_model* m) {
   m->pfAO = (__half*)(m->rarena + o_pao);
   m->pfH = (__half*)(m->rarena + o_ph);
   m->pfTok = (uint32_t*)(m->rarena + o_pt);
+  m->sample_scratch = m->rarena + o_ss;
   m->sync_words = (uint32_t*)(m->rarena + o_sw);
   m->desc_full = (StepDesc*)(m->rarena + o_df);
   m->desc_nohead = (StepDesc*)(m->rarena + o_dn);
@@ -1218,6 +1221,24 @@ int nfai_decode_greedy(nfai_model* m, uint32_t first_token, int n_steps, uint32_
 int nfai_model_get_hparams(const nfai_model* m, nfai_hparams* out) {
   if (!m || !out) return fail(m ? m->ctx : nullptr, NFAI_ERR_ARG, "null argument");
   *out = m->hp;
+  return NFAI_OK;
+}
+
+int nfai_sample_top_p(nfai_model* m, float temperature, float top_p, int top_k, float u, uint32_t* token_out) {
+  int rc = ready(m);
+  if (rc) return rc;
+  nfai_ctx* c = m->ctx;
+  if (!token_out || !(temperature > 0.f) || !(top_p > 0.f) || top_k < 1 || top_k > 64 || !(u >= 0.f && u < 1.f))
+    return fail(c, NFAI_ERR_ARG, "bad sampling parameters (temperature > 0, top_p > 0, 1 <= top_k <= 64, 0 <= u < 1)");
+  if (c->world != 1) return fail(c, NFAI_ERR_STATE, "on-device sampling needs the whole vocabulary on one GPU");
+  if (m->pos == 0) return fail(c, NFAI_ERR_STATE, "no step has produced logits yet");
+  uint32_t* dev_tok = c->dev_err + 8;
+  CU(c, launch_sample_top_p(c->stream, m->logits, m->hp.V, &m->state->last_argmax, &m->state->cur_token, temperature, top_p,
+                            top_k, u, m->sample_scratch, dev_tok));
+  CU(c, cudaMemcpyAsync(c->pin_small + 16, dev_tok, 4, cudaMemcpyDeviceToHost, c->stream));
+  CU(c, cudaStreamSynchronize(c->stream));
+  if (c->pin_small[16] == 0xffffffffu) return fail(c, NFAI_ERR_STATE, "the logits buffer and the step's arg-max are out of step");
+  *token_out = c->pin_small[16];
   return NFAI_OK;
 }
 
@@ -1611,6 +1632,19 @@ int nfai_op_lm_head(nfai_ctx* c, const void* W, int dtype, const float* x, const
   cudaError_t e = launch_gemv(c->stream, dtype, NFAI_F32, EPI_LOGITS, p, t, false);
   if (e == cudaSuccess) e = launch_argmax_final(c->stream, p.part_val, p.part_idx, nparts, nullptr, argmax_out, nullptr, 0, PrefetchPlan(), nullptr, 0, false);
   cudaFreeAsync(pv, c->stream);
+  return op_end(c, e);
+}
+
+int nfai_op_sample_top_p(nfai_ctx* c, const float* logits, uint32_t V, float temperature, float top_p, int top_k, float u,
+                         uint32_t* token_out) {
+  int rc = op_begin(c);
+  if (rc) return rc;
+  if (!logits || !token_out || !V || !(temperature > 0.f) || !(top_p > 0.f) || top_k < 1 || top_k > 64 || !(u >= 0.f && u < 1.f))
+    return fail(c, NFAI_ERR_ARG, "bad argument");
+  void* scratch = nullptr;
+  CU(c, cudaMallocAsync(&scratch, sample_scratch_bytes(V, nullptr), c->stream));
+  cudaError_t e = launch_sample_top_p(c->stream, logits, V, nullptr, nullptr, temperature, top_p, top_k, u, scratch, token_out);
+  cudaFreeAsync(scratch, c->stream);
   return op_end(c, e);
 }
 

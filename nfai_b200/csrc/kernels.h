@@ -131,6 +131,13 @@ cudaError_t launch_argmax_final(cudaStream_t s, const float* part_val, const uin
 // xchg_epoch (may be null) counts the tensor-parallel exchanges completed on this context; a step adds its own.
 cudaError_t launch_advance(cudaStream_t s, StepState* state, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl);
 
+// Temperature / top-k / top-p sampling of `logits` (V floats) on the device. `argmax` points at the index of the
+// largest logit (null: found by an extra kernel). Writes the chosen token to *token_out and, if given, *cur_token;
+// 0xffffffff when `argmax` does not belong to these logits.
+size_t sample_scratch_bytes(uint32_t V, int* nslices_out);
+cudaError_t launch_sample_top_p(cudaStream_t s, const float* logits, uint32_t V, const uint32_t* argmax, uint32_t* cur_token,
+                                float temperature, float top_p, int top_k, float u, void* scratch, uint32_t* token_out);
+
 // Scatter/convert one uploaded chunk into a matrix's final place: source element g = elem_off + e sits at
 // (row, col) = (g / K, g % K); rows [row_lo,row_hi) x cols [col_lo,col_hi) are kept and land at
 // dst[((row-row_lo)*row_mul + row_off) * ldd + (col-col_lo)].

@@ -22,6 +22,7 @@
 //  * An untied LM head (output.weight) is used when present; the reference always ties
 //    (NFAI.Models.Llama3/LlamaModel.cs:64-67).
 //  * A position >= ctx is an error instead of an out-of-bounds write.
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -496,3 +497,48 @@ void orc_op_attention(const float* q, const float* kc, const float* vc, uint32_t
 void orc_op_silu_mul(const float* gate, const float* up, uint32_t F, float* h) { silu_mul(gate, up, F, h); }
 
 }  // extern "C"
+
+// ---- sampling ------------------------------------------------------------------------------------------------
+// Temperature / top-k / top-p sampling exactly as NFAI.Models.Llama3/SamplingUtils.cs:5-33, with the uniform
+// random number passed in (the reference draws it from Random.Shared): scaled = logit / T; probabilities by
+// Softmax (:35-41: max, MathF.Exp(l - max), LINQ Sum = double accumulation returned as float, e / sum); stable sort
+// by probability descending; the first top_k; accumulate until the cumulative probability reaches top_p;
+// renormalise (LINQ Sum again); return the first index whose running sum exceeds u, else the last one.
+extern "C" uint32_t orc_sample_top_p(const float* logits, uint64_t V, float temperature, float top_p, int top_k, float u) {
+  std::vector<float> scaled(V);
+  for (uint64_t i = 0; i < V; ++i) scaled[i] = logits[i] / temperature;
+  float mx = scaled[0];
+  for (uint64_t i = 1; i < V; ++i) mx = scaled[i] > mx ? scaled[i] : mx;
+  std::vector<float> e(V);
+  double sum = 0.0;
+  for (uint64_t i = 0; i < V; ++i) {
+    e[i] = expf(scaled[i] - mx);
+    sum += (double)e[i];
+  }
+  const float sumf = (float)sum;
+  std::vector<uint32_t> order(V);
+  for (uint64_t i = 0; i < V; ++i) order[i] = (uint32_t)i;
+  std::vector<float> prob(V);
+  for (uint64_t i = 0; i < V; ++i) prob[i] = e[i] / sumf;
+  // OrderByDescending is a stable sort: equal probabilities keep their index order
+  std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return prob[a] > prob[b]; });
+  const uint64_t k = (uint64_t)top_k < V ? (uint64_t)top_k : V;
+  std::vector<uint32_t> idx;
+  std::vector<float> pr;
+  float cumulative = 0.f;
+  for (uint64_t i = 0; i < k; ++i) {
+    cumulative += prob[order[i]];
+    idx.push_back(order[i]);
+    pr.push_back(prob[order[i]]);
+    if (cumulative >= top_p) break;
+  }
+  double tot = 0.0;
+  for (float p : pr) tot += (double)p;
+  const float total = (float)tot;
+  float running = 0.f;
+  for (size_t i = 0; i < pr.size(); ++i) {
+    running += pr[i] / total;
+    if (u < running) return idx[i];
+  }
+  return idx.back();
+}

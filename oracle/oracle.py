@@ -76,6 +76,8 @@ def lib() -> C.CDLL:
     L.orc_op_attention.argtypes = [fp, fp, fp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, fp,
                                    C.c_int]
     L.orc_op_silu_mul.argtypes = [fp, fp, C.c_uint32, fp]
+    L.orc_sample_top_p.restype = C.c_uint32
+    L.orc_sample_top_p.argtypes = [fp, C.c_uint64, C.c_float, C.c_float, C.c_int, C.c_float]
     _lib = L
     return L
 
@@ -250,3 +252,9 @@ def silu_mul(gate, up) -> np.ndarray:
     h = np.empty_like(gate)
     lib().orc_op_silu_mul(_fp(gate), _fp(up), gate.size, _fp(h))
     return h
+
+
+def sample_top_p(logits, temperature: float = 0.5, top_p: float = 0.95, top_k: int = 40, u: float = 0.5) -> int:
+    """NFAI.Models.Llama3/SamplingUtils.cs:5-33 with the uniform random number `u` supplied by the caller."""
+    logits = _f32(logits)
+    return int(lib().orc_sample_top_p(_fp(logits), logits.size, temperature, top_p, top_k, u))

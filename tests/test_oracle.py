@@ -144,3 +144,48 @@ def test_oracle_reproduces_golden(oracle, key):
         tk = oracle.argmax(m.decode(tk))
         greedy.append(tk)
     assert np.array_equal(np.array(greedy, np.uint32), g["greedy"])
+
+
+# ---- sampling (NFAI.Models.Llama3/SamplingUtils.cs:5-33) ----------------------------------------------------
+
+def _np_top_p(logits, T, top_p, top_k, u):
+    """Independent restatement in numpy (float64 where LINQ's Sum is double)."""
+    s = (logits.astype(np.float32) / np.float32(T)).astype(np.float32)
+    e = np.exp((s - s.max()).astype(np.float32)).astype(np.float32)
+    p = (e / np.float32(e.astype(np.float64).sum())).astype(np.float32)
+    order = np.argsort(-p, kind="stable")[:top_k]
+    keep, cum = [], np.float32(0)
+    for i in order:
+        cum = np.float32(cum + p[i])
+        keep.append(i)
+        if cum >= np.float32(top_p):
+            break
+    tot = np.float32(p[keep].astype(np.float64).sum())
+    run = np.float32(0)
+    for i in keep:
+        run = np.float32(run + np.float32(p[i] / tot))
+        if np.float32(u) < run:
+            return int(i)
+    return int(keep[-1])
+
+
+def test_sample_top_p_matches_numpy(oracle):
+    rng = np.random.default_rng(5)
+    for V in (7, 300, 4096):
+        logits = (rng.standard_normal(V) * 3).astype(np.float32)
+        for u in (0.0, 0.03, 0.4, 0.77, 0.999):
+            for (T, p, k) in ((0.5, 0.95, 40), (1.0, 0.5, 5), (2.0, 1.5, 64)):
+                assert oracle.sample_top_p(logits, T, p, min(k, 64), u) == _np_top_p(logits, T, p, k, u)
+
+
+def test_sample_top_p_edges(oracle):
+    # a peaked distribution always yields its peak; u = 0 yields the arg-max; ties keep index order
+    logits = np.full(100, -30.0, np.float32)
+    logits[42] = 10.0
+    for u in (0.0, 0.5, 0.999):
+        assert oracle.sample_top_p(logits, u=u) == 42
+    flat = np.zeros(10, np.float32)
+    assert oracle.sample_top_p(flat, 1.0, 1.0, 10, 0.0) == 0
+    assert oracle.sample_top_p(flat, 1.0, 1.0, 10, 0.95) == 9
+    assert oracle.sample_top_p(flat, 1.0, 1.0, 3, 0.99) == 2     # top_k cuts the flat tail in index order
+    assert oracle.sample_top_p(flat, 1.0, 0.25, 10, 0.99) == 2   # 0.1+0.1+0.1 >= 0.25 stops after three
