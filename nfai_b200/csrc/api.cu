@@ -188,13 +188,14 @@ void read_tune(const char* name, GemvTune& t, int r_default, int u_default) {
   std::string key = std::string("NFAI_TUNE_") + name;
   const char* v = getenv(key.c_str());
   if (v) {
-    int r = 0, u = 0, cps = 0, mode = 0;
-    int got = sscanf(v, "%d,%d,%d,%d", &r, &u, &cps, &mode);
+    int r = 0, u = 0, cps = 0, mode = 0, split = 0;
+    int got = sscanf(v, "%d,%d,%d,%d,%d", &r, &u, &cps, &mode, &split);
     if (got >= 2 && (r == 1 || r == 2 || r == 4) && (u == 2 || u == 3 || u == 4 || u == 6 || u == 8)) {
       t.rows_per_warp = r;
       t.unroll = u;
       if (got >= 3 && cps >= 1 && cps <= 16) t.ctas_per_sm = cps;
       if (got >= 4 && (mode == 0 || mode == 1)) t.mode = mode;
+      if (got >= 5 && (split == 0 || split == 1 || split == 2 || split == 4 || split == 8)) t.split = split;
     }
   }
 }

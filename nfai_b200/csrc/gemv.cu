@@ -25,23 +25,34 @@ using namespace gemv_detail;
 
 namespace {
 
+constexpr int kSmemHeader = 96;  // floats ahead of x in shared memory: reduction scratch and split-row partials
+
 // ---- the streamer ---------------------------------------------------------------------------------------------
 template <typename WT, typename KVT, int R, int U, int EPI>
 __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(16) float smem[];
-  float* red = smem;      // 2*kWarps words of reduction scratch
-  float* xs = smem + 32;  // K floats of x, then K floats of gain
+  float* red = smem;                  // 2*kWarps words of reduction scratch
+  float* part = smem + 32;            // [2][kWarps][R] partial row sums of a split row block (two parities)
+  float* xs = smem + kSmemHeader;     // K floats of x, then K floats of gain
   constexpr int VE = WeightVec<WT>::kElems;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t nvec = p.K / VE;  // host guarantees K % VE == 0 and 16-byte aligned rows
-  const uint32_t nkb = (nvec + 32 * U - 1) / (32 * U);  // batches per row block
-  const uint32_t nrb = (p.N + R - 1) / R;                // row blocks
+  // A work item is (row block, K chunk): R rows x cv vectors. With split = 1 the chunk is the whole row.
+  const uint32_t sl = p.split_log2, S = 1u << sl;
+  const uint32_t cv = (((nvec + S - 1) >> sl) + 31u) & ~31u;  // vectors per chunk, a whole number of warp strides
+  const uint32_t nkb = (cv + 32 * U - 1) / (32 * U);          // batches per item
+  const uint32_t nrb = (p.N + R - 1) / R;                     // row blocks
+  const uint32_t nitems = nrb << sl;
   const uint32_t TW = gridDim.x * kWarps;
+  const uint32_t nrounds = (nitems + TW - 1) / TW;  // the same for every warp of the grid: barriers stay uniform
   const WT* const Wbase = reinterpret_cast<const WT*>(p.W);
   const uint4 zero = make_uint4(0, 0, 0, 0);
 
-  auto load_batch = [&](uint4(&buf)[U][R], uint32_t rb, uint32_t kb) {
-    if (rb >= nrb) return;
+  auto load_batch = [&](uint4(&buf)[U][R], uint32_t t, uint32_t kb) {
+    if (t >= nitems) return;
+    const uint32_t rb = t >> sl, c = t & (S - 1);
+    const uint32_t v0 = c * cv + kb * (32 * U) + lane;
+    const uint32_t vend = min((c + 1) * cv, nvec);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       uint32_t n = rb * R + r;
@@ -49,15 +60,15 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
       const uint4* wrow = reinterpret_cast<const uint4*>(Wbase + (size_t)n * p.K);
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        uint32_t v = kb * (32 * U) + lane + 32 * u;
-        buf[u][r] = v < nvec ? ld_stream16(wrow + v) : zero;
+        const uint32_t v = v0 + 32 * u;
+        buf[u][r] = v < vend ? ld_stream16(wrow + v) : zero;
       }
     }
   };
 
-  uint32_t rb = blockIdx.x * kWarps + warp, kb = 0;
+  uint32_t t = blockIdx.x * kWarps + warp;
   uint4 cur[U][R];
-  load_batch(cur, rb, 0);  // weights do not depend on the previous kernel
+  load_batch(cur, t, 0);  // weights do not depend on the previous kernel
   load_gain(p, xs);
   prefetch_plan(p.pf, kPrefetchChunk);
   pdl_launch_dependents();
@@ -69,50 +80,69 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
   float acc[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) acc[r] = 0.f;
-  while (rb < nrb) {
-    uint32_t nrb_next = rb, nkb_next = kb + 1;
-    if (nkb_next == nkb) {
-      nkb_next = 0;
-      nrb_next = rb + TW;
-    }
-    uint4 nxt[U][R];
-    load_batch(nxt, nrb_next, nkb_next);
+  for (uint32_t round = 0; round < nrounds; ++round, t += TW) {
+    const uint32_t c = t & (S - 1);
+    const uint32_t vend = min((c + 1) * cv, nvec);
+    for (uint32_t kb = 0; kb < nkb; ++kb) {
+      uint4 nxt[U][R];
+      const bool last = kb + 1 == nkb;
+      load_batch(nxt, last ? t + TW : t, last ? 0u : kb + 1);
+      if (t < nitems) {
+        const uint32_t v0 = c * cv + kb * (32 * U) + lane;
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      uint32_t v = kb * (32 * U) + lane + 32 * u;
-      if (v < nvec) {
-        float xv[VE];
-        const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)v * VE);
+        for (int u = 0; u < U; ++u) {
+          const uint32_t v = v0 + 32 * u;
+          if (v < vend) {
+            float xv[VE];
+            const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)v * VE);
 #pragma unroll
-        for (int i = 0; i < VE / 4; ++i) {
-          float4 t = xp[i];
-          xv[4 * i] = t.x;
-          xv[4 * i + 1] = t.y;
-          xv[4 * i + 2] = t.z;
-          xv[4 * i + 3] = t.w;
-        }
+            for (int i = 0; i < VE / 4; ++i) {
+              float4 q = xp[i];
+              xv[4 * i] = q.x;
+              xv[4 * i + 1] = q.y;
+              xv[4 * i + 2] = q.z;
+              xv[4 * i + 3] = q.w;
+            }
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-          float wf[VE];
-          WeightVec<WT>::unpack(cur[u][r], wf);
+            for (int r = 0; r < R; ++r) {
+              float wf[VE];
+              WeightVec<WT>::unpack(cur[u][r], wf);
 #pragma unroll
-          for (int i = 0; i < VE; ++i) acc[r] = fmaf(wf[i], xv[i], acc[r]);
+              for (int i = 0; i < VE; ++i) acc[r] = fmaf(wf[i], xv[i], acc[r]);
+            }
+          }
         }
       }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int r = 0; r < R; ++r) cur[u][r] = nxt[u][r];
     }
-    if (nkb_next == 0) {  // the row block is complete
+    // the item is complete
 #pragma unroll
-      for (int r = 0; r < R; ++r) acc[r] = warp_sum(acc[r]);
-      row_epilogue<KVT, R, EPI>(p, rb * R, acc, best_v, best_i);
+    for (int r = 0; r < R; ++r) acc[r] = warp_sum(acc[r]);
+    if (S == 1) {
+      if (t < nitems) row_epilogue<KVT, R, EPI>(p, t * R, acc, best_v, best_i);
+    } else {
+      // the S chunks of a row block sit in S consecutive warps of this CTA: add them up in warp order
+      float* pr = part + (round & 1) * (kWarps * R);
+      if (lane == 0) {
 #pragma unroll
-      for (int r = 0; r < R; ++r) acc[r] = 0.f;
+        for (int r = 0; r < R; ++r) pr[warp * R + r] = acc[r];
+      }
+      __syncthreads();
+      if (c == 0 && t < nitems) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          float a = pr[warp * R + r];
+          for (uint32_t j = 1; j < S; ++j) a += pr[(warp + j) * R + r];
+          acc[r] = a;
+        }
+        row_epilogue<KVT, R, EPI>(p, (t >> sl) * R, acc, best_v, best_i);
+      }
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-      for (int r = 0; r < R; ++r) cur[u][r] = nxt[u][r];
-    rb = nrb_next;
-    kb = nkb_next;
+    for (int r = 0; r < R; ++r) acc[r] = 0.f;
   }
   if constexpr (EPI == EPI_LOGITS) cta_argmax_partial(p, best_v, best_i, red);
 }
@@ -122,7 +152,7 @@ template <typename WT, typename KVT, int EPI>
 __global__ void __launch_bounds__(kThreads) gemv_scalar_kernel(const GemvParams p) {
   extern __shared__ __align__(16) float smem[];
   float* red = smem;
-  float* xs = smem + 32;
+  float* xs = smem + kSmemHeader;
   constexpr int R = 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t nrb = (p.N + R - 1) / R;
@@ -234,17 +264,35 @@ static bool use_ring(int wdtype, GemvEpilogue epi, const GemvParams& p, const Ge
   return true;
 }
 
+// How many warps share one row block (1, 2, 4 or 8; returned as log2). Splitting gives every warp of the
+// persistent grid the same small amount of work when the matrix has few rows (down and O projections: 2048 rows
+// of up to 16 KB), which is what keeps the whole matrix in flight at once; matrices with many rows do not need it.
+static uint32_t gemv_split_log2(int wdtype, bool vec, int R, const GemvParams& p, const GemvTune& t) {
+  if (!vec) return 0;
+  if (t.split == 1 || t.split == 2 || t.split == 4 || t.split == 8) return t.split == 1 ? 0 : t.split == 2 ? 1 : t.split == 4 ? 2 : 3;
+  const uint32_t ve = wdtype == 1 ? 8 : 4;
+  const uint32_t per_lane = p.K / ve / 32;  // 16-byte vectors per lane per row
+  const uint32_t nrb = (p.N + R - 1) / R;
+  const uint32_t warps = kNumSMs * (uint32_t)(t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm) * kWarps;
+  uint32_t sl = 0;
+  while (sl < 3 && (per_lane >> sl) > (uint32_t)t.unroll && (nrb << sl) < 8 * warps) ++sl;
+  return sl;
+}
+
 uint32_t gemv_grid(int wdtype, GemvEpilogue epi, const GemvParams& p, const GemvTune& t) {
   int ring_R = 0;
   if (use_ring(wdtype, epi, p, t, &ring_R)) return gemv_ring_grid(p, ring_R, t.ctas_per_sm);
-  const uint32_t per_cta = kWarps * rows_per_warp(epi, vector_ok(wdtype, p), t);
-  const uint32_t want = (p.N + per_cta - 1) / per_cta;
-  const uint32_t cap = kNumSMs * (uint32_t)(t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm);  // persistent: warps loop over row blocks
+  const bool vec = vector_ok(wdtype, p);
+  const int R = rows_per_warp(epi, vec, t);
+  const uint32_t nitems = ((p.N + R - 1) / R) << gemv_split_log2(wdtype, vec, R, p, t);
+  const uint32_t want = (nitems + kWarps - 1) / kWarps;
+  const uint32_t cap = kNumSMs * (uint32_t)(t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm);  // persistent: warps loop over items
   return want < cap ? want : cap;
 }
 
-cudaError_t launch_gemv(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue epi, const GemvParams& p,
+cudaError_t launch_gemv(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue epi, const GemvParams& p_in,
                         const GemvTune& t, bool pdl) {
+  GemvParams p = p_in;
   if (p.N == 0 || p.K == 0) return cudaErrorInvalidValue;
   if ((epi == EPI_QKV_ROPE || epi == EPI_SILU_MUL) && (p.N % 2) != 0) return cudaErrorInvalidValue;
   int ring_R = 0;
@@ -253,7 +301,8 @@ cudaError_t launch_gemv(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue ep
   const bool vec = vector_ok(wdtype, p);
   const int R = rows_per_warp(epi, vec, t);
   dim3 grid(gemv_grid(wdtype, epi, p, t));
-  size_t smem = (32 + (size_t)p.K * (p.gain ? 2 : 1)) * sizeof(float);
+  p.split_log2 = gemv_split_log2(wdtype, vec, R, p, t);
+  size_t smem = (kSmemHeader + (size_t)p.K * (p.gain ? 2 : 1)) * sizeof(float);
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
   if (wdtype == 1) {
     if (kvdtype == 1) return launch_e<__half, __half>(epi, vec, R, t.unroll, grid, smem, s, pdl, p);

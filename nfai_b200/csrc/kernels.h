@@ -67,6 +67,7 @@ struct GemvParams {
   uint32_t* part_idx = nullptr;
   PrefetchPlan pf;
   uint32_t* err = nullptr;  // optional device word for error bits when there is no StepState (4 = a bounded wait gave up)
+  uint32_t split_log2 = 0;  // filled in by launch_gemv: log2 of the warps that share one row block
 };
 
 // Tunable launch shape of the GEMV family.
@@ -75,6 +76,7 @@ struct GemvTune {
   int rows_per_warp = 2;  // mode 0: 1, 2 or 4; mode 1: 1 or 2 (EPI_QKV_ROPE and EPI_SILU_MUL need an even value)
   int unroll = 4;         // mode 0: 16-byte loads in flight per row per lane (2, 4 or 8); mode 1: ring stages (2, 3, 4, 6)
   int ctas_per_sm = 2;    // persistent grid = min(needed, 148 * ctas_per_sm) CTAs of 256 threads
+  int split = 0;          // mode 0: warps sharing one row block (1, 2, 4, 8); 0 = chosen from the matrix shape
 };
 
 size_t gemv_ring_smem(const GemvParams& p, int R, int S);
