@@ -61,106 +61,24 @@ struct KV8<__half> {
   }
 };
 
-// One CTA of NW warps: KV head / head group `bx`, split `s` of a sequence of `seq` positions. Every thread of the
-// CTA must call it (it uses block barriers); it returns early, uniformly, when the split is not active.
-// CG = true reads q, K and V with L2-only loads (needed when the caller wrote them earlier in the same kernel).
-// kG = query heads that share one pass over K and V (fewer heads, fewer registers).
-template <typename KVT, int D, int NW, bool CG, int kG, int UNR_ = 0>
-__device__ __forceinline__ void attn_core(const AttnParams& p, const uint32_t bx, const uint32_t s, const uint32_t seq,
-                                          const uint32_t min_chunk) {
+// Second half of the attention of one CTA: every lane holds an online-softmax state (m, l, acc) over its own
+// positions for up to kG query heads; merge lanes -> warps -> (if the sequence was split) CTAs, and write the output.
+// Every thread of the CTA must call it (block barriers).
+template <int D, int NW, int kG>
+__device__ __forceinline__ void attn_finish(const AttnParams& p, const uint32_t bx, const uint32_t s, const uint32_t S_eff,
+                                            const uint32_t h0, const uint32_t nh, float (&m)[kG], float (&l)[kG],
+                                            float (&acc)[kG][8]) {
   constexpr int kAT = NW * 32;
   constexpr int kAW = NW;
   constexpr int LPP = D / 8;    // lanes per position
-  constexpr int PPW = 32 / LPP; // positions per warp step
-  constexpr int UNR = UNR_ > 0 ? UNR_ : KV8<KVT>::kUnroll;  // steps whose K and V are requested together
   constexpr int STR = D + 2;    // one partial in scratch: D accumulators, m, l
   constexpr int SSTR = D + 4;   // the same in shared memory, padded so that every row stays 16-byte aligned
-
   __shared__ __align__(16) float wpart[kAW][kG][SSTR];  // per-warp partials
   __shared__ float fin_scale[kAW][kG];
   __shared__ float fin_ML[kG][2];
   __shared__ uint32_t is_last;
-
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int grp = lane / LPP, sub = lane % LPP;
-  const uint32_t G = p.qH / p.kvH;
-  const uint32_t hgroups = (G + kG - 1) / kG;
-  const uint32_t g = bx / hgroups;
-  const uint32_t hg = bx % hgroups;
-  const uint32_t h0 = g * G + hg * kG;
-  const uint32_t nh = min((uint32_t)kG, G - hg * kG);
-  const uint32_t kvDim = p.kvH * D;
-  uint32_t chunk = (seq + p.S_max - 1) / p.S_max;
-  chunk = chunk < min_chunk ? min_chunk : chunk;
-  chunk = (chunk + 63) / 64 * 64;
-  const uint32_t S_eff = (seq + chunk - 1) / chunk;
-  if (s >= S_eff) return;
-  const uint32_t t0 = s * chunk;
-  const uint32_t t1 = min(seq, t0 + chunk);
-
-  // this lane's eight dims of the (up to) four query heads
-  float q[kG][8];
-#pragma unroll
-  for (int j = 0; j < kG; ++j) {
-    if (j < (int)nh) {
-      const float* qp = p.q + (h0 + j) * D + sub * 8;
-      float4 a = CG ? __ldcg(reinterpret_cast<const float4*>(qp)) : *reinterpret_cast<const float4*>(qp);
-      float4 b = CG ? __ldcg(reinterpret_cast<const float4*>(qp + 4)) : *reinterpret_cast<const float4*>(qp + 4);
-      q[j][0] = a.x; q[j][1] = a.y; q[j][2] = a.z; q[j][3] = a.w;
-      q[j][4] = b.x; q[j][5] = b.y; q[j][6] = b.z; q[j][7] = b.w;
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) q[j][e] = 0.f;
-    }
-  }
-  const float scale = 1.0f / sqrtf((float)D);  // AttentionScoreCalculationShader.cs:112
-  float m[kG], l[kG], acc[kG][8];
-#pragma unroll
-  for (int j = 0; j < kG; ++j) {
-    m[j] = kNegBig;
-    l[j] = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[j][e] = 0.f;
-  }
-  const KVT* kc = reinterpret_cast<const KVT*>(p.kcache) + g * D + sub * 8;
-  const KVT* vc = reinterpret_cast<const KVT*>(p.vcache) + g * D + sub * 8;
-
-  for (uint32_t base = t0 + warp * PPW; base < t1; base += kAW * PPW * UNR) {
-    typename KV8<KVT>::Raw kr[UNR], vr[UNR];
-    bool valid[UNR];
-#pragma unroll
-    for (int u = 0; u < UNR; ++u) {
-      const uint32_t t = base + u * (kAW * PPW) + grp;
-      valid[u] = t < t1;
-      kr[u] = valid[u] ? KV8<KVT>::template ld<CG>(kc + (size_t)t * kvDim) : KV8<KVT>::zero();
-      vr[u] = valid[u] ? KV8<KVT>::template ld<CG>(vc + (size_t)t * kvDim) : KV8<KVT>::zero();
-    }
-#pragma unroll
-    for (int u = 0; u < UNR; ++u) {
-      if (base + u * (kAW * PPW) >= t1) break;  // warp-uniform
-      float kf[8], vf[8];
-      KV8<KVT>::unpack(kr[u], kf);
-      KV8<KVT>::unpack(vr[u], vf);
-#pragma unroll
-      for (int j = 0; j < kG; ++j) {
-        float dot = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) dot = fmaf(q[j][e], kf[e], dot);
-#pragma unroll
-        for (int o = 1; o < LPP; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        if (valid[u]) {
-          const float sc = dot * scale;
-          const float m_new = fmaxf(m[j], sc);
-          const float alpha = __expf(m[j] - m_new);
-          const float pr = __expf(sc - m_new);
-          l[j] = fmaf(l[j], alpha, pr);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[j][e] = fmaf(acc[j][e], alpha, pr * vf[e]);
-          m[j] = m_new;
-        }
-      }
-    }
-  }
 
   // ---- merge the lane groups of the warp (same dims, different positions)
 #pragma unroll
@@ -254,6 +172,103 @@ __device__ __forceinline__ void attn_core(const AttnParams& p, const uint32_t bx
     p.out[(h0 + j) * D + i] = O * (1.0f / Lsum);
   }
   if (tid == 0) p.tickets[bx] = 0;  // ready for the next launch
+}
+
+// One CTA of NW warps: KV head / head group `bx`, split `s` of a sequence of `seq` positions. Every thread of the
+// CTA must call it (it uses block barriers); it returns early, uniformly, when the split is not active.
+// CG = true reads q, K and V with L2-only loads (needed when the caller wrote them earlier in the same kernel).
+// kG = query heads that share one pass over K and V (fewer heads, fewer registers).
+template <typename KVT, int D, int NW, bool CG, int kG, int UNR_ = 0>
+__device__ __forceinline__ void attn_core(const AttnParams& p, const uint32_t bx, const uint32_t s, const uint32_t seq,
+                                          const uint32_t min_chunk) {
+  constexpr int kAT = NW * 32;
+  constexpr int kAW = NW;
+  constexpr int LPP = D / 8;    // lanes per position
+  constexpr int PPW = 32 / LPP; // positions per warp step
+  constexpr int UNR = UNR_ > 0 ? UNR_ : KV8<KVT>::kUnroll;  // steps whose K and V are requested together
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int grp = lane / LPP, sub = lane % LPP;
+  const uint32_t G = p.qH / p.kvH;
+  const uint32_t hgroups = (G + kG - 1) / kG;
+  const uint32_t g = bx / hgroups;
+  const uint32_t hg = bx % hgroups;
+  const uint32_t h0 = g * G + hg * kG;
+  const uint32_t nh = min((uint32_t)kG, G - hg * kG);
+  const uint32_t kvDim = p.kvH * D;
+  uint32_t chunk = (seq + p.S_max - 1) / p.S_max;
+  chunk = chunk < min_chunk ? min_chunk : chunk;
+  chunk = (chunk + 63) / 64 * 64;
+  const uint32_t S_eff = (seq + chunk - 1) / chunk;
+  if (s >= S_eff) return;
+  const uint32_t t0 = s * chunk;
+  const uint32_t t1 = min(seq, t0 + chunk);
+
+  // this lane's eight dims of the (up to) four query heads
+  float q[kG][8];
+#pragma unroll
+  for (int j = 0; j < kG; ++j) {
+    if (j < (int)nh) {
+      const float* qp = p.q + (h0 + j) * D + sub * 8;
+      float4 a = CG ? __ldcg(reinterpret_cast<const float4*>(qp)) : *reinterpret_cast<const float4*>(qp);
+      float4 b = CG ? __ldcg(reinterpret_cast<const float4*>(qp + 4)) : *reinterpret_cast<const float4*>(qp + 4);
+      q[j][0] = a.x; q[j][1] = a.y; q[j][2] = a.z; q[j][3] = a.w;
+      q[j][4] = b.x; q[j][5] = b.y; q[j][6] = b.z; q[j][7] = b.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q[j][e] = 0.f;
+    }
+  }
+  const float scale = 1.0f / sqrtf((float)D);  // AttentionScoreCalculationShader.cs:112
+  float m[kG], l[kG], acc[kG][8];
+#pragma unroll
+  for (int j = 0; j < kG; ++j) {
+    m[j] = kNegBig;
+    l[j] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[j][e] = 0.f;
+  }
+  const KVT* kc = reinterpret_cast<const KVT*>(p.kcache) + g * D + sub * 8;
+  const KVT* vc = reinterpret_cast<const KVT*>(p.vcache) + g * D + sub * 8;
+
+  for (uint32_t base = t0 + warp * PPW; base < t1; base += kAW * PPW * UNR) {
+    typename KV8<KVT>::Raw kr[UNR], vr[UNR];
+    bool valid[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const uint32_t t = base + u * (kAW * PPW) + grp;
+      valid[u] = t < t1;
+      kr[u] = valid[u] ? KV8<KVT>::template ld<CG>(kc + (size_t)t * kvDim) : KV8<KVT>::zero();
+      vr[u] = valid[u] ? KV8<KVT>::template ld<CG>(vc + (size_t)t * kvDim) : KV8<KVT>::zero();
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      if (base + u * (kAW * PPW) >= t1) break;  // warp-uniform
+      float kf[8], vf[8];
+      KV8<KVT>::unpack(kr[u], kf);
+      KV8<KVT>::unpack(vr[u], vf);
+#pragma unroll
+      for (int j = 0; j < kG; ++j) {
+        float dot = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dot = fmaf(q[j][e], kf[e], dot);
+#pragma unroll
+        for (int o = 1; o < LPP; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (valid[u]) {
+          const float sc = dot * scale;
+          const float m_new = fmaxf(m[j], sc);
+          const float alpha = __expf(m[j] - m_new);
+          const float pr = __expf(sc - m_new);
+          l[j] = fmaf(l[j], alpha, pr);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[j][e] = fmaf(acc[j][e], alpha, pr * vf[e]);
+          m[j] = m_new;
+        }
+      }
+    }
+  }
+
+  attn_finish<D, NW, kG>(p, bx, s, S_eff, h0, nh, m, l, acc);
 }
 
 

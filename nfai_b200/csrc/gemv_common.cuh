@@ -119,6 +119,88 @@ __device__ __forceinline__ void row_epilogue(const GemvParams& p, uint32_t row0,
   }
 }
 
+// ---- the same epilogues with their inputs fetched ahead of time ------------------------------------------------
+// What an epilogue reads besides the row sums (the residual, the position's cos/sin pair) sits in L2; fetched at
+// the moment the row sum is complete it would add a full L2 round trip to the tail of every row block. The
+// streamer asks for it one item ahead and hands it over here. Every lane runs the preload (same address: one
+// broadcast load).
+template <int R, int EPI>
+__device__ __forceinline__ void epi_preload(const GemvParams& p, uint32_t row0, uint32_t pos, float (&pre)[R]) {
+  if constexpr (EPI == EPI_STORE) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const uint32_t n = row0 + r < p.N ? row0 + r : p.N - 1;
+      pre[r] = p.resid ? __ldcg(p.resid + n) : 0.f;
+    }
+  } else if constexpr (EPI == EPI_QKV_ROPE) {
+#pragma unroll
+    for (int r = 0; r < R; r += 2) {
+      const uint32_t n = row0 + r;
+      float2 cs = make_float2(1.f, 0.f);
+      if (n < p.qDim + p.kvDim && n < p.N && pos < p.ctx) {
+        const uint32_t local = n < p.qDim ? n : n - p.qDim;
+        const uint32_t i = local % p.d;
+        if (i < p.ropeDim) cs = __ldg(p.rope_cs + (size_t)pos * (p.ropeDim / 2) + (i >> 1));
+      }
+      pre[r] = cs.x;
+      pre[r + 1] = cs.y;
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < R; ++r) pre[r] = 0.f;
+  }
+}
+
+template <typename KVT, int R, int EPI>
+__device__ __forceinline__ void row_epilogue_pre(const GemvParams& p, uint32_t row0, const float (&acc)[R],
+                                                 const float (&pre)[R], uint32_t pos, float& best_v, uint32_t& best_i) {
+  if ((threadIdx.x & 31) != 0) return;
+  if constexpr (EPI == EPI_STORE) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      uint32_t n = row0 + r;
+      if (n < p.N) p.y[n] = p.resid ? pre[r] + acc[r] : acc[r];
+    }
+  } else if constexpr (EPI == EPI_QKV_ROPE) {
+    static_assert(R % 2 == 0, "RoPE pairs adjacent rows");
+    if (pos >= p.ctx) {
+      if (p.state) atomicOr(&p.state->err, 2u);
+      return;
+    }
+#pragma unroll
+    for (int r = 0; r < R; r += 2) {
+      uint32_t n = row0 + r;
+      if (n >= p.N) break;
+      float a = acc[r], b = acc[r + 1];
+      if (n < p.qDim + p.kvDim) {
+        uint32_t local = n < p.qDim ? n : n - p.qDim;
+        uint32_t i = local % p.d;
+        if (i < p.ropeDim) {
+          const float c = pre[r], sn = pre[r + 1];
+          float v1 = __fsub_rn(__fmul_rn(c, a), __fmul_rn(sn, b));
+          float v2 = __fadd_rn(__fmul_rn(sn, a), __fmul_rn(c, b));
+          a = v1;
+          b = v2;
+        }
+        if (n < p.qDim) {
+          p.q_out[n] = a;
+          p.q_out[n + 1] = b;
+        } else {
+          KVT* kc = reinterpret_cast<KVT*>(p.kcache) + (size_t)pos * p.kvDim + local;
+          store_as(kc, a);
+          store_as(kc + 1, b);
+        }
+      } else {
+        KVT* vc = reinterpret_cast<KVT*>(p.vcache) + (size_t)pos * p.kvDim + (n - p.qDim - p.kvDim);
+        store_as(vc, a);
+        store_as(vc + 1, b);
+      }
+    }
+  } else {
+    row_epilogue<KVT, R, EPI>(p, row0, acc, best_v, best_i);
+  }
+}
+
 // EPI_LOGITS: one (max, lowest index) partial per CTA.
 __device__ __forceinline__ void cta_argmax_partial(const GemvParams& p, float best_v, uint32_t best_i, float* red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
