@@ -131,6 +131,7 @@ struct nfai_model {
   uint32_t* tickets = nullptr;
   uint32_t S_max = 1;
   uint32_t attn_heads = 4;  // query heads per attention CTA in the decode step
+  std::vector<AttnTileMaps> attn_maps;  // per layer, when the decode step uses the tile-staged attention kernel
   StepState* state = nullptr;
   uint32_t* history = nullptr;
   uint32_t* prompt = nullptr;
@@ -180,6 +181,11 @@ size_t kv_layer_elems(const nfai_model* m) { return (size_t)m->hp.ctx * m->kvDim
 int env_int(const char* name, int dflt) {
   const char* v = getenv(name);
   return v && *v ? atoi(v) : dflt;
+}
+
+bool ring_wanted(uint32_t positions) {
+  const int v = env_int("NFAI_ATTN_RING", -1);
+  return v < 0 ? positions > 4096 : v != 0;
 }
 
 void read_tune(const char* name, GemvTune& t, int r_default, int u_default) {
@@ -402,7 +408,8 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     STEP(launch_gemv(s, wdt, kvdt, EPI_QKV_ROPE, gq, m->tune_qkv, pdl));
     AttnParams ga = attn_params(m, l);
     ga.pf = pp.next(end_of(LW.qkv), false);
-    STEP(launch_attn_decode(s, kvdt, ga, pdl));
+    if (!m->attn_maps.empty()) STEP(launch_attn_ring(s, ga, m->attn_maps[l], pdl));
+    else STEP(launch_attn_decode(s, kvdt, ga, pdl));
     GemvParams go = o_params(m, l);
     go.pf = pp.next(end_of(LW.o), true);
     STEP(launch_gemv(s, wdt, kvdt, EPI_STORE, go, m->tune_o, pdl));
@@ -966,6 +973,18 @@ int nfai_model_finalize(nfai_model* m) {
   if (e != cudaSuccess) return fail(c, NFAI_ERR_OOM, "cudaMalloc of %zu run-time bytes (KV cache etc.): %s", off, cudaGetErrorString(e));
   CU(c, cudaMemsetAsync(m->rarena, 0, off, c->stream));
   m->kc = m->rarena + o_kc; m->vc = m->rarena + o_vc;
+  // long float16 caches: attention through tile-staged rings (NFAI_ATTN_RING=0 keeps the register streamer, 1 forces it)
+  m->attn_maps.clear();
+  if (m->attn_heads == 4 && attn_ring_supported(hp.kv_dtype, hp.d) && ring_wanted(hp.ctx)) {
+    m->attn_maps.resize(hp.L);
+    for (uint32_t l = 0; l < hp.L; ++l) {
+      const size_t lo = (size_t)l * kv_layer_elems(m) * kvs;
+      if (attn_ring_make_maps((char*)m->kc + lo, (char*)m->vc + lo, hp.ctx, m->kvDimL, hp.d, &m->attn_maps[l]) != cudaSuccess) {
+        m->attn_maps.clear();  // no tile descriptors on this driver: the register streamer serves every length
+        break;
+      }
+    }
+  }
   m->rope_cs = (float2*)(m->rarena + o_rope);
   m->xbuf = (float*)(m->rarena + o_x);
   m->q = (float*)(m->rarena + o_q);
@@ -1459,7 +1478,9 @@ int nfai_profile_kernel(nfai_model* m, int which, int iters, float* avg_ms, uint
       case 2: return launch_gemv(c->stream, wdt, kvdt, EPI_QKV_ROPE, qkv_params(m, l), m->tune_qkv, false);
       case 3: return launch_gemv(c->stream, wdt, kvdt, EPI_STORE, o_params(m, l), m->tune_o, false);
       case 4: return launch_gemv(c->stream, wdt, kvdt, EPI_LOGITS, head_params(m), m->tune_head, false);
-      default: return launch_attn_decode(c->stream, kvdt, attn_params(m, l), false);
+      default:
+        if (!m->attn_maps.empty()) return launch_attn_ring(c->stream, attn_params(m, l), m->attn_maps[l], false);
+        return launch_attn_decode(c->stream, kvdt, attn_params(m, l), false);
     }
   };
   // the launches are captured into a graph so that short kernels are timed on the device, not at the rate the
@@ -1594,6 +1615,10 @@ int nfai_op_attn_decode(nfai_ctx* c, const float* q, const void* kcache, const v
   size_t tick_off = align_up(attn_part_floats(qH, d, a.S_max) * 4, 256);
   a.tickets = (uint32_t*)((char*)scratch + tick_off);
   CU(c, cudaMemsetAsync(a.tickets, 0, (size_t)kvH * attn_head_groups(qH, kvH) * 4, c->stream));
+  if (attn_ring_supported(kv_dtype, d) && ring_wanted(seq)) {
+    AttnTileMaps maps;
+    if (attn_ring_make_maps(kcache, vcache, seq, kvH * d, d, &maps) == cudaSuccess) return op_end(c, launch_attn_ring(c->stream, a, maps, false));
+  }
   return op_end(c, launch_attn_decode(c->stream, kv_dtype, a, false));
 }
 

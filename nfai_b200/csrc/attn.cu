@@ -65,6 +65,12 @@ cudaError_t launch_p(cudaStream_t s, const AttnParams& p, uint32_t T) {
   return cudaGetLastError();
 }
 
+template <typename Kern>
+cudaError_t launch_cfg(const cudaLaunchConfig_t& cfg, Kern kernel, const AttnParams& p) {
+  apply_step_carveout(kernel);
+  return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 template <typename KVT>
 cudaError_t launch_d(cudaStream_t s, const AttnParams& p, bool pdl) {
   const uint32_t hgroups = attn_head_groups(p.qH, p.kvH, p.heads_per_cta);
@@ -80,24 +86,24 @@ cudaError_t launch_d(cudaStream_t s, const AttnParams& p, bool pdl) {
   cfg.numAttrs = 1;
   if (p.heads_per_cta == 1) {
     switch (p.d) {
-      case 32: return cudaLaunchKernelEx(&cfg, attn_decode_kernel<KVT, 32, 1>, p);
-      case 64: return cudaLaunchKernelEx(&cfg, attn_decode_kernel<KVT, 64, 1>, p);
-      case 128: return cudaLaunchKernelEx(&cfg, attn_decode_kernel<KVT, 128, 1>, p);
+      case 32: return launch_cfg(cfg, attn_decode_kernel<KVT, 32, 1>, p);
+      case 64: return launch_cfg(cfg, attn_decode_kernel<KVT, 64, 1>, p);
+      case 128: return launch_cfg(cfg, attn_decode_kernel<KVT, 128, 1>, p);
       default: return cudaErrorInvalidValue;
     }
   }
   if (p.heads_per_cta == 2) {
     switch (p.d) {
-      case 32: return cudaLaunchKernelEx(&cfg, attn_decode_kernel<KVT, 32, 2>, p);
-      case 64: return cudaLaunchKernelEx(&cfg, attn_decode_kernel<KVT, 64, 2>, p);
-      case 128: return cudaLaunchKernelEx(&cfg, attn_decode_kernel<KVT, 128, 2>, p);
+      case 32: return launch_cfg(cfg, attn_decode_kernel<KVT, 32, 2>, p);
+      case 64: return launch_cfg(cfg, attn_decode_kernel<KVT, 64, 2>, p);
+      case 128: return launch_cfg(cfg, attn_decode_kernel<KVT, 128, 2>, p);
       default: return cudaErrorInvalidValue;
     }
   }
   switch (p.d) {
-    case 32: return cudaLaunchKernelEx(&cfg, attn_decode_kernel<KVT, 32, 4>, p);
-    case 64: return cudaLaunchKernelEx(&cfg, attn_decode_kernel<KVT, 64, 4>, p);
-    case 128: return cudaLaunchKernelEx(&cfg, attn_decode_kernel<KVT, 128, 4>, p);
+    case 32: return launch_cfg(cfg, attn_decode_kernel<KVT, 32, 4>, p);
+    case 64: return launch_cfg(cfg, attn_decode_kernel<KVT, 64, 4>, p);
+    case 128: return launch_cfg(cfg, attn_decode_kernel<KVT, 128, 4>, p);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -15,6 +15,16 @@ inline cudaError_t prefer_max_shared(Kern kernel) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
 }
 
+// One shared-memory carve-out (percent of the SM's 228 KB) for every kernel of the decode step, so that consecutive
+// kernels never make an SM re-partition L1 and shared memory between them. Environment NFAI_CARVEOUT; negative or
+// unset = every kernel keeps the driver's own choice.
+int step_carveout_pct();
+template <typename Kern>
+inline void apply_step_carveout(Kern kernel) {
+  const int pct = step_carveout_pct();
+  if (pct >= 0) cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, pct > 100 ? 100 : pct);
+}
+
 // Device-resident state of one model: the graph's kernels read and advance it so that one captured graph
 // serves every position.
 struct StepState {
@@ -121,6 +131,18 @@ cudaError_t launch_attn_decode(cudaStream_t s, int kvdtype, const AttnParams& p,
 // Causal attention of T prompt tokens: token t (q row t of p.q, [T][qH*d]) attends to positions 0 .. p.seq_imm-1+t;
 // output rows go to p.out_half ([T][qH*d] float16). One CTA per (KV head group, token), no split.
 cudaError_t launch_attn_prefill(cudaStream_t s, int kvdtype, const AttnParams& p, uint32_t T);
+
+// Long-context variant for a float16 cache (d = 64 or 128, four query heads per CTA): K and V staged through
+// shared-memory rings by 2-D tile copies. The two tile descriptors (one K, one V per layer) are built on the host.
+struct AttnTileMaps {
+  alignas(64) unsigned char k[128];
+  alignas(64) unsigned char v[128];
+};
+bool attn_ring_supported(int kvdtype, uint32_t d);
+size_t attn_ring_smem(int stages);
+cudaError_t attn_ring_make_maps(const void* kcache, const void* vcache, uint32_t ctx, uint32_t kvDim, uint32_t d,
+                                AttnTileMaps* out);
+cudaError_t launch_attn_ring(cudaStream_t s, const AttnParams& p, const AttnTileMaps& maps, bool pdl);
 
 cudaError_t launch_embed(cudaStream_t s, int wdtype, const void* E, uint32_t H, uint32_t V, StepState* state,
                          const uint32_t* prompt, uint32_t token_imm, float* x_out, const PrefetchPlan& pf, bool pdl);

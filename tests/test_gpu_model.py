@@ -306,3 +306,24 @@ def test_full_size_1b_properties(factory, oracle):
     assert ms > 0 and nbytes == 2 * cfg.F * cfg.H * 2 + cfg.H * 4
     assert m.step_launches() == 3 + 5 * cfg.L
     m.Dispose()
+
+
+@pytest.mark.parametrize("key", ["s3", "s2"])
+def test_long_cache_attention_ignores_stale_rows(factory, oracle, monkeypatch, key):
+    """A cache longer than 4096 positions selects the tile-staged attention kernel; rows past the sequence hold
+    NaN here and must not leak into the result."""
+    cfg = synth.get_config(key)
+    n = 20
+    toks = synth.prompt_ids(cfg, n, 0)
+    ref = oracle.OracleModel(cfg, ctx=n).load_synthetic(0)
+    m = make(cfg, 4200, factory, kv_dtype="f16")
+    nan = np.full(cfg.kvDim, np.nan, np.float32)
+    for l in range(cfg.L):
+        for pos in list(range(0, 40)) + [4199]:
+            m.write_kv(l, pos, nan, nan)
+    for t in toks:
+        want = ref.decode(int(t))
+        got, am = m.decode(int(t))
+        assert np.isfinite(got).all()
+        assert float(np.abs(got - want).max()) <= ABS_F16
+    m.Dispose()

@@ -225,3 +225,34 @@ def test_argmax_ties_pick_the_lowest_index(cuda_ctx, oracle):
     dW = dev(W)
     call(cuda_ctx, "nfai_op_lm_head", ptr(dW), _lib.F32, ptr(dx), None, C.c_float(0), H, V, ptr(logits), ptr(am))
     assert int(host(am)[0]) == 0
+
+
+@pytest.mark.parametrize("qH,kvH,d", [(32, 8, 64), (24, 8, 128), (4, 2, 64), (8, 1, 64), (6, 2, 128)])
+@pytest.mark.parametrize("seq", [1, 2, 15, 16, 17, 100, 700, 5000, 20000])
+def test_attention_tile_staged_kernel_every_length(cuda_ctx, oracle, monkeypatch, qH, kvH, d, seq):
+    """The long-context kernel (K and V through shared-memory rings) forced on for every length of a float16 cache."""
+    if seq == 20000 and (qH, kvH, d) not in ((32, 8, 64), (24, 8, 128)):
+        pytest.skip("the longest sequence on two geometries only")
+    monkeypatch.setenv("NFAI_ATTN_RING", "1")
+    rng = np.random.default_rng(seq * 17 + d + qH)
+    kvDim = kvH * d
+    q = rng.standard_normal(qH * d).astype(np.float32)
+    kc = rng.standard_normal((seq, kvDim)).astype(np.float16)
+    vc = rng.standard_normal((seq, kvDim)).astype(np.float16)
+    want = oracle.attention(q, kc.astype(np.float32), vc.astype(np.float32), seq, qH, kvH, d, 1e-5)
+    lib = _lib.load()
+    nbytes = lib.nfai_op_attn_scratch_bytes(qH, kvH, d, seq)
+    scratch = torch.zeros(nbytes // 4 + 1, dtype=torch.float32, device="cuda")
+    dq, dk, dv = dev(q), dev(kc), dev(vc)
+    out = torch.empty(qH * d, dtype=torch.float32, device="cuda")
+    for _ in range(2):
+        out.zero_()
+        call(cuda_ctx, "nfai_op_attn_decode", ptr(dq), ptr(dk), ptr(dv), _lib.F16, seq, qH, kvH, d, ptr(out), ptr(scratch),
+             C.c_size_t(nbytes))
+        assert rel_err(host(out), want) < TOL
+    # the register-streaming kernel gives the same answer on the same inputs
+    monkeypatch.setenv("NFAI_ATTN_RING", "0")
+    out2 = torch.empty(qH * d, dtype=torch.float32, device="cuda")
+    call(cuda_ctx, "nfai_op_attn_decode", ptr(dq), ptr(dk), ptr(dv), _lib.F16, seq, qH, kvH, d, ptr(out2), ptr(scratch),
+         C.c_size_t(nbytes))
+    assert rel_err(host(out2), host(out)) < TOL
