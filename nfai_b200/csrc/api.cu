@@ -165,6 +165,8 @@ struct nfai_model {
   float* pfQ = nullptr;       // [chunk][qDim] rotated queries
   __half* pfAO = nullptr;     // [chunk][qDim] attention output
   __half* pfH = nullptr;      // [chunk][F] SiLU(gate)*up
+  float* pfPart = nullptr;    // split-K partial tiles of the prompt GEMMs
+  size_t pfPartFloats = 0;
   uint32_t* pfTok = nullptr;  // [chunk]
   // L2 look-ahead: how far beyond the weights a kernel consumes the step's weight sequence is requested
   uint64_t pf_look = 0, pf_extra = 0;
@@ -960,6 +962,9 @@ int nfai_model_finalize(nfai_model* m) {
   const size_t o_pao = take((size_t)pfc * m->qDimL * 2);
   const size_t o_ph = take((size_t)pfc * m->Fl * 2);
   const size_t o_pt = take((size_t)pfc * 4 + 4);
+  // split-K happens only below 120 output tiles of 128 x 128, with at most 148 CTAs: 148 tiles of partials bound it
+  const size_t pf_part_floats = want_pf && env_int("NFAI_GEMM_SPLIT", 1) ? (size_t)148 * 128 * 128 * 2 : 0;
+  const size_t o_pp = take(pf_part_floats * 4);
   const size_t o_ss = take(sample_scratch_bytes(m->Vl, nullptr));
   const size_t o_sw = take(64);
   const size_t o_df = take(sizeof(StepDesc));
@@ -1008,6 +1013,8 @@ int nfai_model_finalize(nfai_model* m) {
   m->pfAO = (__half*)(m->rarena + o_pao);
   m->pfH = (__half*)(m->rarena + o_ph);
   m->pfTok = (uint32_t*)(m->rarena + o_pt);
+  m->pfPart = pf_part_floats ? (float*)(m->rarena + o_pp) : nullptr;
+  m->pfPartFloats = pf_part_floats;
   m->sample_scratch = m->rarena + o_ss;
   m->sync_words = (uint32_t*)(m->rarena + o_sw);
   m->desc_full = (StepDesc*)(m->rarena + o_df);
@@ -1159,6 +1166,7 @@ static int prefill_batched(nfai_model* m, const uint32_t* tokens, int n) {
       CU(c, launch_rmsnorm_to_half(s, m->pfX0, L.attn_norm.ptr, hp.eps, T, hp.H, m->pfA));
       GemmEpilogue eq;
       eq.kind = GEMM_EPI_QKV_ROPE;
+      eq.scratch = m->pfPart; eq.scratch_floats = m->pfPartFloats;
       eq.out_f32 = m->pfQ; eq.kcache = kcl; eq.vcache = vcl; eq.kv_f16 = kvdt == NFAI_F16;
       eq.qDim = m->qDimL; eq.kvDim = m->kvDimL; eq.d = hp.d; eq.ropeDim = hp.ropeDim; eq.pos0 = pos0; eq.rope_cs = m->rope_cs;
       CU(c, launch_gemm_tc(s, m->pfA, (const __half*)L.qkv.ptr, T, m->qDimL + 2 * m->kvDimL, hp.H, eq, err));
@@ -1168,13 +1176,16 @@ static int prefill_batched(nfai_model* m, const uint32_t* tokens, int n) {
       CU(c, launch_attn_prefill(s, kvdt, a, T));
       GemmEpilogue eo;
       eo.kind = GEMM_EPI_STORE; eo.out_f32 = m->pfX1; eo.resid = m->pfX0;
+      eo.scratch = m->pfPart; eo.scratch_floats = m->pfPartFloats;
       CU(c, launch_gemm_tc(s, m->pfAO, (const __half*)L.o.ptr, T, hp.H, m->qDimL, eo, err));
       CU(c, launch_rmsnorm_to_half(s, m->pfX1, L.ffn_norm.ptr, hp.eps, T, hp.H, m->pfA));
       GemmEpilogue eg;
       eg.kind = GEMM_EPI_SILU_MUL; eg.out_f16 = m->pfH;
+      eg.scratch = m->pfPart; eg.scratch_floats = m->pfPartFloats;
       CU(c, launch_gemm_tc(s, m->pfA, (const __half*)L.gateup.ptr, T, 2 * m->Fl, hp.H, eg, err));
       GemmEpilogue ed;
       ed.kind = GEMM_EPI_STORE; ed.out_f32 = m->pfX0; ed.resid = m->pfX1;
+      ed.scratch = m->pfPart; ed.scratch_floats = m->pfPartFloats;
       CU(c, launch_gemm_tc(s, m->pfH, (const __half*)L.down.ptr, T, hp.H, m->Fl, ed, err));
       if (last_chunk)  // the last token's residual stream after this block, where the taps and the LM head expect it
         CU(c, cudaMemcpyAsync(x_in(m, l + 1), m->pfX0 + (size_t)(T - 1) * hp.H, (size_t)hp.H * 4, cudaMemcpyDeviceToDevice, s));
@@ -1632,7 +1643,14 @@ int nfai_op_gemm_f16(nfai_ctx* c, const void* A, const void* W, uint32_t M, uint
   GemmEpilogue ep;
   ep.kind = GEMM_EPI_STORE;
   ep.out_f32 = C;
-  rc = op_end(c, launch_gemm_tc(c->stream, (const __half*)A, (const __half*)W, M, N, K, ep, c->dev_err));
+  const uint32_t Z = env_int("NFAI_GEMM_SPLIT", 1) ? gemm_tc_splits(M, N, K) : 1;
+  if (Z > 1) {
+    ep.scratch_floats = (size_t)Z * M * N;
+    CU(c, cudaMallocAsync((void**)&ep.scratch, ep.scratch_floats * 4, c->stream));
+  }
+  cudaError_t e = launch_gemm_tc(c->stream, (const __half*)A, (const __half*)W, M, N, K, ep, c->dev_err);
+  if (ep.scratch) cudaFreeAsync(ep.scratch, c->stream);
+  rc = op_end(c, e);
   if (rc) return rc;
   uint32_t err = 0;
   CU(c, cudaMemcpy(&err, c->dev_err, 4, cudaMemcpyDeviceToHost));

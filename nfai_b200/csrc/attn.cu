@@ -67,7 +67,6 @@ cudaError_t launch_p(cudaStream_t s, const AttnParams& p, uint32_t T) {
 
 template <typename Kern>
 cudaError_t launch_cfg(const cudaLaunchConfig_t& cfg, Kern kernel, const AttnParams& p) {
-  apply_step_carveout(kernel);
   return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 

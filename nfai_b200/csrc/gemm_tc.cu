@@ -107,74 +107,94 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// ---- epilogues: 32 consecutive output columns [n0, n0+32) of row m ---------------------------------------------
-__device__ __forceinline__ void epilogue_cols(const GemmEpilogue& ep, uint32_t m, uint32_t n0, uint32_t N, const float (&v)[32]) {
+// ---- epilogues: two adjacent output columns (n, n+1) of row m; n is even -----------------------------------------
+__device__ __forceinline__ void epilogue_pair(const GemmEpilogue& ep, uint32_t m, uint32_t n, uint32_t N, float a, float b) {
   switch (ep.kind) {
     case GEMM_EPI_STORE: {
       float* out = ep.out_f32 + (size_t)m * N;
       const float* res = ep.resid ? ep.resid + (size_t)m * N : nullptr;
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (n0 + i < N) out[n0 + i] = res ? res[n0 + i] + v[i] : v[i];
+      out[n] = res ? res[n] + a : a;
+      if (n + 1 < N) out[n + 1] = res ? res[n + 1] + b : b;
       break;
     }
     case GEMM_EPI_SILU_MUL: {  // columns (2j, 2j+1) = (gate_j, up_j); h_j = up * silu(gate), stored as float16
-      __half* out = ep.out_f16 + (size_t)m * (N / 2);
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        if (n0 + i + 1 < N) {
-          const float gate = v[i], up = v[i + 1];
-          const float sig = __fdiv_rn(1.0f, 1.0f + expf(-gate));
-          out[(n0 + i) >> 1] = __float2half_rn(__fmul_rn(up, __fmul_rn(gate, sig)));
-        }
+      if (n + 1 < N) {
+        const float sig = __fdiv_rn(1.0f, 1.0f + expf(-a));
+        ep.out_f16[(size_t)m * (N / 2) + (n >> 1)] = __float2half_rn(__fmul_rn(b, __fmul_rn(a, sig)));
       }
       break;
     }
     case GEMM_EPI_QKV_ROPE: {  // columns [Q | K | V]; RoPE on adjacent pairs at position pos0 + m
       const uint32_t pos = ep.pos0 + m;
-      float* qrow = ep.out_f32 + (size_t)m * ep.qDim;
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        const uint32_t n = n0 + i;
-        if (n >= N) continue;
-        float a = v[i], b = v[i + 1];
-        if (n < ep.qDim + ep.kvDim) {
-          const uint32_t local = n < ep.qDim ? n : n - ep.qDim;
-          const uint32_t e = local % ep.d;
-          if (e < ep.ropeDim) {
-            const float2 cs = ep.rope_cs[(size_t)pos * (ep.ropeDim / 2) + (e >> 1)];
-            const float v1 = __fsub_rn(__fmul_rn(cs.x, a), __fmul_rn(cs.y, b));
-            const float v2 = __fadd_rn(__fmul_rn(cs.y, a), __fmul_rn(cs.x, b));
-            a = v1;
-            b = v2;
-          }
-          if (n < ep.qDim) {
-            qrow[n] = a;
-            qrow[n + 1] = b;
-          } else if (ep.kv_f16) {
-            __half* kc = reinterpret_cast<__half*>(ep.kcache) + (size_t)pos * ep.kvDim + local;
-            kc[0] = __float2half_rn(a);
-            kc[1] = __float2half_rn(b);
-          } else {
-            float* kc = reinterpret_cast<float*>(ep.kcache) + (size_t)pos * ep.kvDim + local;
-            kc[0] = a;
-            kc[1] = b;
-          }
+      if (n < ep.qDim + ep.kvDim) {
+        const uint32_t local = n < ep.qDim ? n : n - ep.qDim;
+        const uint32_t e = local % ep.d;
+        if (e < ep.ropeDim) {
+          const float2 cs = ep.rope_cs[(size_t)pos * (ep.ropeDim / 2) + (e >> 1)];
+          const float v1 = __fsub_rn(__fmul_rn(cs.x, a), __fmul_rn(cs.y, b));
+          const float v2 = __fadd_rn(__fmul_rn(cs.y, a), __fmul_rn(cs.x, b));
+          a = v1;
+          b = v2;
+        }
+        if (n < ep.qDim) {
+          float* qrow = ep.out_f32 + (size_t)m * ep.qDim;
+          qrow[n] = a;
+          qrow[n + 1] = b;
+        } else if (ep.kv_f16) {
+          __half* kc = reinterpret_cast<__half*>(ep.kcache) + (size_t)pos * ep.kvDim + local;
+          kc[0] = __float2half_rn(a);
+          kc[1] = __float2half_rn(b);
         } else {
-          const uint32_t local = n - ep.qDim - ep.kvDim;
-          if (ep.kv_f16) {
-            __half* vc = reinterpret_cast<__half*>(ep.vcache) + (size_t)pos * ep.kvDim + local;
-            vc[0] = __float2half_rn(a);
-            vc[1] = __float2half_rn(b);
-          } else {
-            float* vc = reinterpret_cast<float*>(ep.vcache) + (size_t)pos * ep.kvDim + local;
-            vc[0] = a;
-            vc[1] = b;
-          }
+          float* kc = reinterpret_cast<float*>(ep.kcache) + (size_t)pos * ep.kvDim + local;
+          kc[0] = a;
+          kc[1] = b;
+        }
+      } else {
+        const uint32_t local = n - ep.qDim - ep.kvDim;
+        if (ep.kv_f16) {
+          __half* vc = reinterpret_cast<__half*>(ep.vcache) + (size_t)pos * ep.kvDim + local;
+          vc[0] = __float2half_rn(a);
+          vc[1] = __float2half_rn(b);
+        } else {
+          float* vc = reinterpret_cast<float*>(ep.vcache) + (size_t)pos * ep.kvDim + local;
+          vc[0] = a;
+          vc[1] = b;
         }
       }
       break;
     }
+  }
+}
+
+// 32 consecutive output columns [n0, n0+32) of row m (n0 is a multiple of 32)
+__device__ __forceinline__ void epilogue_cols(const GemmEpilogue& ep, uint32_t m, uint32_t n0, uint32_t N, const float (&v)[32]) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 2)
+    if (n0 + i < N) epilogue_pair(ep, m, n0 + i, N, v[i], v[i + 1]);
+}
+
+// Split-K: raw partial sums of the same 32 columns into [split][M][N]
+__device__ __forceinline__ void partial_cols(float* part, uint32_t m, uint32_t n0, uint32_t N, const float (&v)[32]) {
+  float* out = part + (size_t)m * N + n0;
+#pragma unroll
+  for (int i = 0; i < 32; ++i)
+    if (n0 + i < N) out[i] = v[i];
+}
+
+// Second kernel of a split GEMM: one thread per column pair adds the partials in split order and applies the epilogue.
+__global__ void __launch_bounds__(256) gemm_finish_kernel(const float* __restrict__ part, uint32_t M, uint32_t N, uint32_t Z,
+                                                          const GemmEpilogue ep) {
+  const uint32_t pairs = (N + 1) / 2;
+  const size_t total = (size_t)M * pairs;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const uint32_t m = (uint32_t)(idx / pairs), n = (uint32_t)(idx % pairs) * 2;
+    float a = 0.f, b = 0.f;
+    for (uint32_t z = 0; z < Z; ++z) {
+      const float* p = part + ((size_t)z * M + m) * N + n;
+      a += p[0];
+      if (n + 1 < N) b += p[1];
+    }
+    epilogue_pair(ep, m, n, N, a, b);
   }
 }
 
@@ -201,7 +221,10 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_kernel(const __grid_cons
   const uint32_t full0 = s_u32(bars), empty0 = s_u32(bars + STAGES), accbar = s_u32(bars + 2 * STAGES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
-  const uint32_t KT = (K + kBK - 1) / kBK;
+  // this CTA's share of the K tiles (split-K: blockIdx.z of gridDim.z; every share holds at least one tile)
+  const uint32_t KT_all = (K + kBK - 1) / kBK;
+  const uint32_t kt0 = (uint32_t)((uint64_t)KT_all * blockIdx.z / gridDim.z);
+  const uint32_t KT = (uint32_t)((uint64_t)KT_all * (blockIdx.z + 1) / gridDim.z) - kt0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -231,8 +254,8 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_kernel(const __grid_cons
         }
         const uint32_t a_dst = s_u32(gsm + s * SM::kStage), b_dst = a_dst + SM::kABytes;
         bar_expect_tx(full0 + 8 * s, SM::kABytes + SM::kBBytes);
-        tma_load_2d(a_dst, &mapA, (int)(kt * kBK), (int)m0, full0 + 8 * s);
-        tma_load_2d(b_dst, &mapW, (int)(kt * kBK), (int)n0, full0 + 8 * s);
+        tma_load_2d(a_dst, &mapA, (int)((kt0 + kt) * kBK), (int)m0, full0 + 8 * s);
+        tma_load_2d(b_dst, &mapW, (int)((kt0 + kt) * kBK), (int)n0, full0 + 8 * s);
       }
     }
   } else if (warp == 1) {
@@ -264,7 +287,10 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_kernel(const __grid_cons
       for (int c = 0; c < BN / 32; ++c) {
         float v[32];
         tmem_ld32(tmem_base + ((lane_grp * 32u) << 16) + (uint32_t)c * 32u, v);
-        if (m < M && n0 + c * 32 < N) epilogue_cols(ep, m, n0 + c * 32, N, v);
+        if (m < M && n0 + c * 32 < N) {
+          if (gridDim.z > 1) partial_cols(ep.scratch + (size_t)blockIdx.z * M * N, m, n0 + c * 32, N, v);
+          else epilogue_cols(ep, m, n0 + c * 32, N, v);
+        }
       }
     }
   }
@@ -334,19 +360,36 @@ bool make_map(CUtensorMap* map, const __half* base, uint64_t rows, uint64_t K, u
 
 template <int BN, int STAGES>
 cudaError_t launch_bn(cudaStream_t s, const __half* A, const __half* W, uint32_t M, uint32_t N, uint32_t K,
-                      const GemmEpilogue& ep, uint32_t* err) {
+                      const GemmEpilogue& ep, uint32_t* err, uint32_t Z = 1) {
   CUtensorMap mapA, mapW;
   if (!make_map(&mapA, A, M, K, kBM) || !make_map(&mapW, W, N, K, BN)) return cudaErrorInvalidValue;
   auto kern = gemm_tc_kernel<BN, STAGES>;
   const size_t smem = GemmSmem<BN, STAGES>::kTotal;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  dim3 grid((N + BN - 1) / BN, (M + kBM - 1) / kBM);
+  dim3 grid((N + BN - 1) / BN, (M + kBM - 1) / kBM, Z);
   kern<<<grid, kGemmThreads, smem, s>>>(mapA, mapW, M, N, K, ep, err);
+  e = cudaGetLastError();
+  if (e != cudaSuccess || Z == 1) return e;
+  const size_t pairs = (size_t)M * ((N + 1) / 2);
+  const size_t want = (pairs + 255) / 256;
+  gemm_finish_kernel<<<(unsigned)(want < 1184 ? want : 1184), 256, 0, s>>>(ep.scratch, M, N, Z, ep);
   return cudaGetLastError();
 }
 
 }  // namespace
+
+// A tile grid of fewer than 120 CTAs of 128 x 128 leaves SMs without work (a chunk of <= 128 prompt tokens times a
+// 2048-column matrix is 16 tiles): divide K so that about one CTA per SM streams weights, at least two K tiles each.
+uint32_t gemm_tc_splits(uint32_t M, uint32_t N, uint32_t K) {
+  const uint32_t tiles = ((M + kBM - 1) / kBM) * ((N + 127) / 128);
+  const uint32_t KT = (K + kBK - 1) / kBK;
+  if (tiles >= 120) return 1;
+  uint32_t z = 148 / tiles;
+  if (z > KT / 2) z = KT / 2;
+  if (z > 16) z = 16;
+  return z < 1 ? 1 : z;
+}
 
 cudaError_t launch_gemm_tc(cudaStream_t s, const __half* A, const __half* W, uint32_t M, uint32_t N, uint32_t K,
                            const GemmEpilogue& ep, uint32_t* err) {
@@ -354,6 +397,11 @@ cudaError_t launch_gemm_tc(cudaStream_t s, const __half* A, const __half* W, uin
   if ((ep.kind == GEMM_EPI_SILU_MUL || ep.kind == GEMM_EPI_QKV_ROPE) && (N & 1u)) return cudaErrorInvalidValue;
   // enough CTAs to pull weights with every SM when the chunk is a single row of tiles
   const uint32_t mtiles = (M + kBM - 1) / kBM;
+  if (ep.scratch) {
+    uint32_t Z = gemm_tc_splits(M, N, K);
+    while (Z > 1 && (size_t)Z * M * N > ep.scratch_floats) --Z;
+    if (Z > 1) return launch_bn<128, 4>(s, A, W, M, N, K, ep, err, Z);
+  }
   if (mtiles * ((N + 127) / 128) >= 120) return launch_bn<128, 4>(s, A, W, M, N, K, ep, err);
   if (mtiles * ((N + 63) / 64) >= 120) return launch_bn<64, 6>(s, A, W, M, N, K, ep, err);
   return launch_bn<32, 8>(s, A, W, M, N, K, ep, err);

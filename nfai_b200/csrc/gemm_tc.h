@@ -19,7 +19,15 @@ struct GemmEpilogue {
   int kv_f16 = 0;
   uint32_t qDim = 0, kvDim = 0, d = 0, ropeDim = 0, pos0 = 0;
   const float2* rope_cs = nullptr;
+  // Optional scratch for split-K: when the tile grid alone would leave most SMs idle (a short prompt chunk), the K
+  // range is divided over several CTAs, each stores its float32 partial tile here ([split][M][N]) and a second
+  // kernel adds the partials in split order and applies the epilogue. Without scratch the GEMM never splits.
+  float* scratch = nullptr;
+  size_t scratch_floats = 0;
 };
+
+// Number of K splits launch_gemm_tc would use for this shape given enough scratch (1 = no split).
+uint32_t gemm_tc_splits(uint32_t M, uint32_t N, uint32_t K);
 
 // C = A[M][K] * W[N][K]^T with the epilogue applied; A and W are float16, K contiguous, K % 8 == 0, 16-byte aligned.
 // err (optional device word) gets bit 4 when a bounded wait inside the kernel gave up.

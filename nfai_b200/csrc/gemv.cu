@@ -204,7 +204,6 @@ cudaError_t launch_k(K kernel, dim3 grid, size_t smem, cudaStream_t s, bool pdl,
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  apply_step_carveout(kernel);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kThreads);

@@ -15,16 +15,6 @@ inline cudaError_t prefer_max_shared(Kern kernel) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
 }
 
-// One shared-memory carve-out (percent of the SM's 228 KB) for every kernel of the decode step, so that consecutive
-// kernels never make an SM re-partition L1 and shared memory between them. Environment NFAI_CARVEOUT; negative or
-// unset = every kernel keeps the driver's own choice.
-int step_carveout_pct();
-template <typename Kern>
-inline void apply_step_carveout(Kern kernel) {
-  const int pct = step_carveout_pct();
-  if (pct >= 0) cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, pct > 100 ? 100 : pct);
-}
-
 // Device-resident state of one model: the graph's kernels read and advance it so that one captured graph
 // serves every position.
 struct StepState {

@@ -1,8 +1,6 @@
 // Small kernels around the GEMV/attention pair: token embedding, arg-max finish + state advance, and the
 // upload-side convert/scatter.
 #include "common.cuh"
-#include <stdlib.h>
-
 #include "kernels.h"
 
 namespace nfai {
@@ -125,10 +123,8 @@ cudaError_t launch_embed(cudaStream_t s, int wdtype, const void* E, uint32_t H, 
   uint32_t blocks = (H + 255) / 256;
   cudaLaunchConfig_t cfg = make_cfg(dim3(blocks), dim3(256), s, attr, pdl);
   if (wdtype == 1)
-    apply_step_carveout(embed_kernel<__half>);
     return cudaLaunchKernelEx(&cfg, embed_kernel<__half>, reinterpret_cast<const __half*>(E), H, V, state, prompt,
                               token_imm, x_out, pf);
-  apply_step_carveout(embed_kernel<float>);
   return cudaLaunchKernelEx(&cfg, embed_kernel<float>, reinterpret_cast<const float*>(E), H, V, state, prompt,
                             token_imm, x_out, pf);
 }
@@ -138,7 +134,6 @@ cudaError_t launch_argmax_final(cudaStream_t s, const float* part_val, const uin
                                 const PrefetchPlan& pf, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl) {
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t cfg = make_cfg(dim3(1), dim3(256), s, attr, pdl);
-  apply_step_carveout(argmax_final_kernel);
   return cudaLaunchKernelEx(&cfg, argmax_final_kernel, part_val, part_idx, nparts, state, argmax_out, history,
                             history_cap, pf, xchg_epoch, xchg_per_step);
 }
@@ -146,7 +141,6 @@ cudaError_t launch_argmax_final(cudaStream_t s, const float* part_val, const uin
 cudaError_t launch_advance(cudaStream_t s, StepState* state, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl) {
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t cfg = make_cfg(dim3(1), dim3(32), s, attr, pdl);
-  apply_step_carveout(advance_kernel);
   return cudaLaunchKernelEx(&cfg, advance_kernel, state, xchg_epoch, xchg_per_step);
 }
 
@@ -160,15 +154,6 @@ cudaError_t launch_ingest(cudaStream_t s, int src_dtype, int dst_dtype, const In
   else if (src_dtype == 1 && dst_dtype == 1) ingest_kernel<__half, __half><<<grid, block, 0, s>>>(p);
   else return cudaErrorInvalidValue;
   return cudaGetLastError();
-}
-
-int step_carveout_pct() {
-  static int pct = -2;
-  if (pct == -2) {
-    const char* v = getenv("NFAI_CARVEOUT");
-    pct = v ? atoi(v) : -1;
-  }
-  return pct;
 }
 
 }  // namespace nfai
