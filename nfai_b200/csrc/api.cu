@@ -953,7 +953,11 @@ int nfai_model_finalize(nfai_model* m) {
   // batched prompt workspace
   const bool want_pf = hp.weight_dtype == NFAI_F16 && c->world == 1 && env_int("NFAI_PREFILL_GEMM", 1) != 0 &&
                        hp.H % 8 == 0 && m->qDimL % 8 == 0 && m->Fl % 8 == 0;
-  const uint32_t pfc = want_pf ? (hp.ctx < 256 ? hp.ctx : 256u) : 0;
+  // tokens per pass of the batched prompt path: long passes amortise ~130 launches per pass and fill the GEMM grids
+  uint32_t pf_want = (uint32_t)env_int("NFAI_PREFILL_CHUNK", 2048);
+  if (pf_want < 8) pf_want = 8;
+  if (pf_want > 8192) pf_want = 8192;
+  const uint32_t pfc = want_pf ? (hp.ctx < pf_want ? hp.ctx : pf_want) : 0;
   const uint32_t amax = hp.H > m->qDimL ? hp.H : m->qDimL;
   const size_t o_px0 = take((size_t)pfc * hp.H * 4);
   const size_t o_px1 = take((size_t)pfc * hp.H * 4);
@@ -1173,7 +1177,8 @@ static int prefill_batched(nfai_model* m, const uint32_t* tokens, int n) {
       AttnParams a;
       a.q = m->pfQ; a.kcache = kcl; a.vcache = vcl; a.qH = m->qHl; a.kvH = m->kvHl; a.d = hp.d;
       a.seq_imm = pos0 + 1; a.out_half = m->pfAO;
-      CU(c, launch_attn_prefill(s, kvdt, a, T));
+      if (attn_prefill_tc_supported(hp.d) && env_int("NFAI_PREFILL_ATTN", 1) != 0) CU(c, launch_attn_prefill_tc(s, kvdt, a, T));
+      else CU(c, launch_attn_prefill(s, kvdt, a, T));
       GemmEpilogue eo;
       eo.kind = GEMM_EPI_STORE; eo.out_f32 = m->pfX1; eo.resid = m->pfX0;
       eo.scratch = m->pfPart; eo.scratch_floats = m->pfPartFloats;

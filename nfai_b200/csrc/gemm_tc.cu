@@ -20,6 +20,9 @@
 #include "common.cuh"
 #include "gemm_tc.h"
 
+#include <functional>
+#include <unordered_map>
+
 namespace nfai {
 
 namespace {
@@ -347,15 +350,40 @@ EncodeTiledFn encode_fn() {
 }
 
 // [rows][K] float16, K contiguous; box = 64 halves x box_rows rows, 128-byte swizzle, zero fill outside.
+// A descriptor depends only on (address, rows, K, box rows); a prompt re-uses the same few hundred of them for every
+// chunk, so they are kept per host thread instead of being encoded again at each of ~130 launches per chunk.
+struct MapKey {
+  const void* base;
+  uint64_t rows, K;
+  uint32_t box_rows;
+  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && K == o.K && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<uint64_t>()((uint64_t)(uintptr_t)k.base ^ (k.rows * 0x9E3779B97F4A7C15ull) ^ (k.K << 20) ^ k.box_rows);
+  }
+};
+
 bool make_map(CUtensorMap* map, const __half* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+  static thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{base, rows, K, box_rows};
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *map = it->second;
+    return true;
+  }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {K, rows};
   cuuint64_t strides[1] = {K * 2};
   cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *map);
+  return true;
 }
 
 template <int BN, int STAGES>
@@ -365,8 +393,15 @@ cudaError_t launch_bn(cudaStream_t s, const __half* A, const __half* W, uint32_t
   if (!make_map(&mapA, A, M, K, kBM) || !make_map(&mapW, W, N, K, BN)) return cudaErrorInvalidValue;
   auto kern = gemm_tc_kernel<BN, STAGES>;
   const size_t smem = GemmSmem<BN, STAGES>::kTotal;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static thread_local int attr_device = -1;  // the attribute is per device: set it once per (thread, device)
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
+  if (attr_device != dev) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr_device = dev;
+  }
   dim3 grid((N + BN - 1) / BN, (M + kBM - 1) / kBM, Z);
   kern<<<grid, kGemmThreads, smem, s>>>(mapA, mapW, M, N, K, ep, err);
   e = cudaGetLastError();

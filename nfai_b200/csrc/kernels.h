@@ -121,6 +121,9 @@ cudaError_t launch_attn_decode(cudaStream_t s, int kvdtype, const AttnParams& p,
 // Causal attention of T prompt tokens: token t (q row t of p.q, [T][qH*d]) attends to positions 0 .. p.seq_imm-1+t;
 // output rows go to p.out_half ([T][qH*d] float16). One CTA per (KV head group, token), no split.
 cudaError_t launch_attn_prefill(cudaStream_t s, int kvdtype, const AttnParams& p, uint32_t T);
+// The same contract on the tensor cores (d = 64 or 128): a CTA owns 64 tokens of one head and walks the prefix once.
+bool attn_prefill_tc_supported(uint32_t d);
+cudaError_t launch_attn_prefill_tc(cudaStream_t s, int kvdtype, const AttnParams& p, uint32_t T);
 
 // Long-context variant for a float16 cache (d = 64 or 128, four query heads per CTA): K and V staged through
 // shared-memory rings by 2-D tile copies. The two tile descriptors (one K, one V per layer) are built on the host.

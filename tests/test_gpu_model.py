@@ -97,7 +97,7 @@ def test_golden_fixtures(factory, key):
     m.Dispose()
 
 
-@pytest.mark.parametrize("key,n", [("c0p", 40), ("s3", 40), ("s3", 300), ("s1", 130)])
+@pytest.mark.parametrize("key,n", [("c0p", 40), ("s3", 40), ("s3", 300), ("s1", 130), ("s2", 70), ("s2", 300)])
 def test_prefill_equals_token_by_token(factory, key, n):
     """Float32 models ingest the prompt token by token (identical results); float16 models use the batched
     tensor-core path, whose float16 activations must keep logits and cache rows inside the float16 tolerance."""
@@ -138,8 +138,9 @@ def test_prefill_equals_token_by_token(factory, key, n):
     b.Dispose()
 
 
-def test_batched_prefill_against_oracle(factory, oracle):
-    cfg = synth.get_config("s3", gain_std=0.1)
+@pytest.mark.parametrize("key", ["s3", "s2"])
+def test_batched_prefill_against_oracle(factory, oracle, key):
+    cfg = synth.get_config(key, gain_std=0.1)
     n = 280  # more than one chunk of 256 tokens
     toks = synth.prompt_ids(cfg, n, 2)
     ref = oracle.OracleModel(cfg, ctx=n + 8).load_synthetic(0)
@@ -327,3 +328,22 @@ def test_long_cache_attention_ignores_stale_rows(factory, oracle, monkeypatch, k
         assert np.isfinite(got).all()
         assert float(np.abs(got - want).max()) <= ABS_F16
     m.Dispose()
+
+
+def test_prompt_in_several_passes_equals_one_pass(monkeypatch):
+    """A prompt longer than the pass length is ingested in several passes; later passes attend to the cache rows of
+    the earlier ones."""
+    cfg = synth.get_config("s3", gain_std=0.1)
+    toks = synth.prompt_ids(cfg, 150, 4)
+    out = {}
+    for chunk in ("64", "2048"):
+        monkeypatch.setenv("NFAI_PREFILL_CHUNK", chunk)
+        f = LlamaModelFactory(0)
+        m = create_synthetic_model(cfg, 160, factory=f)
+        logits, am = m.prefill(toks)
+        out[chunk] = (logits, am, m.read_kv(1, 149), m.read_hidden(1))
+        m.Dispose()
+        f.Dispose()
+    assert float(np.abs(out["64"][0] - out["2048"][0]).max()) <= 2e-3
+    assert rel_err(out["64"][2][0], out["2048"][2][0]) <= 2e-3 and rel_err(out["64"][2][1], out["2048"][2][1]) <= 2e-3
+    assert rel_err(out["64"][3], out["2048"][3]) <= 2e-3
