@@ -20,6 +20,8 @@
 #include "common.cuh"
 #include "gemm_tc.h"
 
+#include <stdlib.h>
+
 #include <functional>
 #include <unordered_map>
 
@@ -116,8 +118,18 @@ __device__ __forceinline__ void epilogue_pair(const GemmEpilogue& ep, uint32_t m
     case GEMM_EPI_STORE: {
       float* out = ep.out_f32 + (size_t)m * N;
       const float* res = ep.resid ? ep.resid + (size_t)m * N : nullptr;
-      out[n] = res ? res[n] + a : a;
-      if (n + 1 < N) out[n + 1] = res ? res[n + 1] + b : b;
+      if ((N & 1u) == 0) {  // rows start on an 8-byte boundary: one store per pair
+        float2 r = make_float2(a, b);
+        if (res) {
+          const float2 q = *reinterpret_cast<const float2*>(res + n);
+          r.x += q.x;
+          r.y += q.y;
+        }
+        *reinterpret_cast<float2*>(out + n) = r;
+      } else {
+        out[n] = res ? res[n] + a : a;
+        if (n + 1 < N) out[n + 1] = res ? res[n + 1] + b : b;
+      }
       break;
     }
     case GEMM_EPI_SILU_MUL: {  // columns (2j, 2j+1) = (gate_j, up_j); h_j = up * silu(gate), stored as float16
@@ -305,6 +317,153 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_kernel(const __grid_cons
   }
 }
 
+// ---- persistent variant: 128 x 256 tiles, two accumulators in tensor memory ------------------------------------
+// A 128 x 128 tile needs 32 KB of operands per 262 tensor-pipe cycles (125 B/clk per SM, about what L2 delivers), so
+// the kernel above is fed at half speed; a 128 x 256 tile needs 48 KB per 524 cycles. One CTA per SM walks tiles
+// blockIdx.x, + gridDim.x, ... (token tiles fastest, so that CTAs running together share one weight tile); the
+// accumulator alternates between two 256-column halves of tensor memory, so the epilogue of tile i (tcgen05.ld,
+// fused epilogue, global stores) runs while the tensor pipe is already on tile i + 1.
+constexpr int kPBN = 256;
+constexpr int kPStages = 4;
+struct PSmem {
+  static constexpr uint32_t kABytes = kBM * kBK * 2;
+  static constexpr uint32_t kBBytes = kPBN * kBK * 2;
+  static constexpr uint32_t kStage = kABytes + kBBytes;
+  static constexpr uint32_t kBarOff = kPStages * kStage;
+  static constexpr uint32_t kEpiOff = kBarOff + 256;             // 4 warps x 32 x 33 floats: accumulator block turned
+  static constexpr uint32_t kEpiBytes = 4 * 32 * 33 * 4;         // so that lanes run along a row of the output
+  static constexpr uint32_t kTotal = kEpiOff + kEpiBytes + 1024;
+};
+
+__device__ __forceinline__ void bar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(kGemmThreads) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap mapA,
+                                                                          const __grid_constant__ CUtensorMap mapW, uint32_t M,
+                                                                          uint32_t N, uint32_t K, const GemmEpilogue ep,
+                                                                          uint32_t* err) {
+  using SM = PSmem;
+  constexpr int STAGES = kPStages;
+  extern __shared__ unsigned char gsm_raw[];
+  unsigned char* gsm = reinterpret_cast<unsigned char*>(((uintptr_t)gsm_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(gsm + SM::kBarOff);
+  // bars: [0, S) full, [S, 2S) empty, [2S, 2S+2) accumulator full, [2S+2, 2S+4) accumulator empty; then the TMEM base word
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  const uint32_t full0 = s_u32(bars), empty0 = s_u32(bars + STAGES), tfull0 = s_u32(bars + 2 * STAGES),
+                 tempty0 = s_u32(bars + 2 * STAGES + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t KT = (K + kBK - 1) / kBK;
+  const uint32_t mtiles = (M + kBM - 1) / kBM, ntiles = (N + kPBN - 1) / kPBN, tiles = mtiles * ntiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      bar_init(full0 + 8 * s, 1);
+      bar_init(empty0 + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      bar_init(tfull0 + 8 * a, 1);
+      bar_init(tempty0 + 8 * a, 4);  // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const uint32_t m0 = (tile % mtiles) * kBM, n0 = (tile / mtiles) * kPBN;
+        for (uint32_t kt = 0; kt < KT; ++kt, ++it) {
+          const uint32_t s = it % STAGES;
+          if (it >= (uint32_t)STAGES) {
+            if (!bar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1)) { ok = false; break; }
+          }
+          const uint32_t a_dst = s_u32(gsm + s * SM::kStage), b_dst = a_dst + SM::kABytes;
+          bar_expect_tx(full0 + 8 * s, SM::kABytes + SM::kBBytes);
+          tma_load_2d(a_dst, &mapA, (int)(kt * kBK), (int)m0, full0 + 8 * s);
+          tma_load_2d(b_dst, &mapW, (int)(kt * kBK), (int)n0, full0 + 8 * s);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(kPBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      uint32_t it = 0, i = 0;
+      for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++i) {
+        const uint32_t acc = i & 1;
+        if (i >= 2) {  // the epilogue must have drained this half of tensor memory (tile i - 2)
+          if (!bar_wait(tempty0 + 8 * acc, ((i >> 1) - 1) & 1)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        const uint32_t d = tmem_base + acc * (uint32_t)kPBN;
+        for (uint32_t kt = 0; kt < KT; ++kt, ++it) {
+          const uint32_t s = it % STAGES;
+          if (!bar_wait(full0 + 8 * s, (it / STAGES) & 1)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_s = s_u32(gsm + s * SM::kStage), b_s = a_s + SM::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            umma_f16(d, smem_desc_sw128(a_s + k * 32), smem_desc_sw128(b_s + k * 32), idesc, (kt | (uint32_t)k) != 0);
+          }
+          umma_commit(empty0 + 8 * s);
+        }
+        if (ok) umma_commit(tfull0 + 8 * acc);
+      }
+    }
+  } else {
+    const uint32_t lane_grp = (uint32_t)(warp & 3);
+    uint32_t i = 0;
+    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++i) {
+      const uint32_t acc = i & 1;
+      const uint32_t m0 = (tile % mtiles) * kBM, n0 = (tile / mtiles) * kPBN;
+      ok = bar_wait(tfull0 + 8 * acc, (i >> 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // tcgen05.ld hands every lane one accumulator row; stores along a row would touch 32 different rows per
+      // instruction. The 32 x 32 block goes through shared memory (row stride 33: conflict-free both ways) and comes
+      // back with lanes 0-15 on the column pairs of one row and lanes 16-31 on the next row: 128-byte coalesced rows.
+      float* eb = reinterpret_cast<float*>(gsm + SM::kEpiOff) + (warp - 2) * (32 * 33);
+#pragma unroll 1
+      for (int c = 0; c < kPBN / 32; ++c) {
+        float v[32];
+        tmem_ld32(tmem_base + ((lane_grp * 32u) << 16) + acc * (uint32_t)kPBN + (uint32_t)c * 32u, v);
+        if (m0 + lane_grp * 32 < M && n0 + c * 32 < N) {  // warp-uniform
+#pragma unroll
+          for (int i = 0; i < 32; ++i) eb[lane * 33 + i] = v[i];
+          __syncwarp();
+          const uint32_t col = 2u * (lane & 15);
+#pragma unroll 4
+          for (int rr = 0; rr < 16; ++rr) {
+            const uint32_t row = 2u * rr + (lane >> 4);
+            const uint32_t m = m0 + lane_grp * 32 + row, n = n0 + c * 32 + col;
+            if (m < M && n < N) epilogue_pair(ep, m, n, N, eb[row * 33 + col], eb[row * 33 + col + 1]);
+          }
+          __syncwarp();
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) bar_arrive(tempty0 + 8 * acc);
+    }
+  }
+  if (!ok && lane == 0 && err) atomicOr(err, 4u);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
 // ---- small producers of the float16 A operands ----------------------------------------------------------------
 __global__ void __launch_bounds__(256) rmsnorm_to_half_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                                               float eps, uint32_t H, __half* __restrict__ out) {
@@ -412,6 +571,24 @@ cudaError_t launch_bn(cudaStream_t s, const __half* A, const __half* W, uint32_t
   return cudaGetLastError();
 }
 
+cudaError_t launch_persistent(cudaStream_t s, const __half* A, const __half* W, uint32_t M, uint32_t N, uint32_t K,
+                              const GemmEpilogue& ep, uint32_t* err) {
+  CUtensorMap mapA, mapW;
+  if (!make_map(&mapA, A, M, K, kBM) || !make_map(&mapW, W, N, K, kPBN)) return cudaErrorInvalidValue;
+  static thread_local int attr_device = -1;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (attr_device != dev) {
+    e = cudaFuncSetAttribute(gemm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PSmem::kTotal);
+    if (e != cudaSuccess) return e;
+    attr_device = dev;
+  }
+  const uint32_t tiles = ((M + kBM - 1) / kBM) * ((N + kPBN - 1) / kPBN);
+  gemm_tc_persistent_kernel<<<tiles < 148 ? tiles : 148, kGemmThreads, PSmem::kTotal, s>>>(mapA, mapW, M, N, K, ep, err);
+  return cudaGetLastError();
+}
+
 }  // namespace
 
 // A tile grid of fewer than 120 CTAs of 128 x 128 leaves SMs without work (a chunk of <= 128 prompt tokens times a
@@ -432,6 +609,9 @@ cudaError_t launch_gemm_tc(cudaStream_t s, const __half* A, const __half* W, uin
   if ((ep.kind == GEMM_EPI_SILU_MUL || ep.kind == GEMM_EPI_QKV_ROPE) && (N & 1u)) return cudaErrorInvalidValue;
   // enough CTAs to pull weights with every SM when the chunk is a single row of tiles
   const uint32_t mtiles = (M + kBM - 1) / kBM;
+  // enough 128 x 256 tiles to occupy most SMs: the persistent kernel (NFAI_GEMM_PERSISTENT=0 keeps the tile-per-CTA one)
+  static const bool persistent_ok = [] { const char* v = getenv("NFAI_GEMM_PERSISTENT"); return !(v && atoi(v) == 0); }();
+  if (persistent_ok && mtiles * ((N + 255) / 256) >= 96) return launch_persistent(s, A, W, M, N, K, ep, err);
   if (ep.scratch) {
     uint32_t Z = gemm_tc_splits(M, N, K);
     while (Z > 1 && (size_t)Z * M * N > ep.scratch_floats) --Z;
