@@ -62,6 +62,48 @@ def make(key: str):
     print(key, "greedy head:", greedy[:8])
 
 
+# Sampling (SamplingUtils.TopP): seeded logits vectors and, for a grid of (temperature, top_p, top_k, u), the token
+# the oracle draws. Only well-conditioned draws are kept (every comparison the algorithm makes has a margin far above
+# the last-bit differences between exponential implementations), so that the device may be held to them exactly.
+SAMPLE_V = (300, 4096, 128256)
+SAMPLE_PARAMS = ((0.5, 0.95, 40), (1.0, 0.5, 5), (2.0, 1.5, 64), (0.7, 0.9, 1))
+
+
+def sample_margin(logits, T, top_p, top_k, u):
+    s = logits.astype(np.float64) / T
+    p = np.exp(s - s.max())
+    p /= p.sum()
+    order = np.argsort(-p, kind="stable")[:top_k]
+    cum = np.cumsum(p[order])
+    m = np.abs(cum - top_p).min()
+    n = int(np.argmax(cum >= top_p)) + 1 if (cum >= top_p).any() else len(order)
+    run = np.cumsum(p[order[:n]] / p[order[:n]].sum())
+    m = min(m, np.abs(run - u).min())
+    d = np.diff(-p[order])
+    if (d > 0).any():
+        m = min(m, (d[d > 0] / p[order][:-1][d > 0]).min())
+    return m
+
+
+def sample_logits(V: int) -> np.ndarray:
+    return (np.random.default_rng(1000 + V).standard_normal(V) * 2.5).astype(np.float32)
+
+
+def make_sampling():
+    rows = []
+    for V in SAMPLE_V:
+        logits = sample_logits(V)
+        us = np.random.default_rng(V).random(8, dtype=np.float32).tolist() + [0.0]
+        for (T, p, k) in SAMPLE_PARAMS:
+            for u in us:
+                if sample_margin(logits, T, p, k, u) < 1e-4:
+                    continue
+                rows.append((V, T, p, k, u, O.sample_top_p(logits, T, p, k, u)))
+    np.savez_compressed(os.path.join(HERE, "sample_top_p.npz"), cases=np.array(rows, np.float64))
+    print("sampling cases:", len(rows))
+
+
 if __name__ == "__main__":
     for k in CASES:
         make(k)
+    make_sampling()

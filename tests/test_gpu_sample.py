@@ -108,3 +108,15 @@ def test_model_sampling_needs_logits(oracle):
         m.sample_top_p()
     m.Dispose()
     factory.Dispose()
+
+
+def test_sampling_golden(cuda_ctx):
+    """The committed draws of the oracle (tests/golden/sample_top_p.npz) reproduced on the device."""
+    import os
+    from tests.golden.make_golden import sample_logits
+    cases = np.load(os.path.join(os.path.dirname(__file__), "golden", "sample_top_p.npz"))["cases"]
+    cache = {}
+    for V, T, p, k, u, tok in cases:
+        V = int(V)
+        logits = cache.setdefault(V, sample_logits(V))
+        assert _sample(cuda_ctx, logits, float(T), float(p), int(k), float(np.float32(u))) == int(tok)

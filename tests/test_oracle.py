@@ -189,3 +189,14 @@ def test_sample_top_p_edges(oracle):
     assert oracle.sample_top_p(flat, 1.0, 1.0, 10, 0.95) == 9
     assert oracle.sample_top_p(flat, 1.0, 1.0, 3, 0.99) == 2     # top_k cuts the flat tail in index order
     assert oracle.sample_top_p(flat, 1.0, 0.25, 10, 0.99) == 2   # 0.1+0.1+0.1 >= 0.25 stops after three
+
+
+def test_sampling_golden(oracle):
+    from tests.golden.make_golden import sample_logits
+    cases = np.load(os.path.join(GOLDEN, "sample_top_p.npz"))["cases"]
+    assert len(cases) > 60
+    cache = {}
+    for V, T, p, k, u, tok in cases:
+        V = int(V)
+        logits = cache.setdefault(V, sample_logits(V))
+        assert oracle.sample_top_p(logits, float(T), float(p), int(k), float(np.float32(u))) == int(tok)
