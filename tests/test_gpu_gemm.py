@@ -11,7 +11,7 @@ torch = pytest.importorskip("torch")
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 32, 128), (1, 32, 64), (17, 96, 256), (128, 3072, 2048),
                                    (200, 2048, 2048), (512, 16384, 2048), (300, 2048, 8192), (64, 520, 72),
                                    (1024, 4096, 4096), (33, 77, 512), (8, 2048, 8192),
-                                   (1000, 3000, 2048), (1024, 16384, 256), (1024, 16384, 128), (2048, 2048, 512)])
+                                   (1000, 3000, 2048), (2048, 8192, 3072), (1024, 16384, 256), (1024, 16384, 128), (2048, 2048, 512)])
 def test_gemm_f16(cuda_ctx, M, N, K):
     rng = np.random.default_rng(M * 131 + N * 7 + K)
     A = (rng.standard_normal((M, K)) * 0.5).astype(np.float16)
