@@ -71,6 +71,8 @@ __global__ void __launch_bounds__(kPThreads) attn_prefill_tc_kernel(const AttnPa
   constexpr int LD = D + 8;  // shared-memory row stride in halves (16 bytes of padding)
   __shared__ __align__(16) __half Ks[kPN * LD];
   __shared__ __align__(16) __half Vs[kPN * LD];
+  pdl_launch_dependents();
+  pdl_wait();  // q and the chunk's cache rows come from the QKV GEMM launched just before
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qr = lane >> 2, qc = (lane & 3) * 2;
   const uint32_t h = blockIdx.y;
@@ -234,11 +236,10 @@ template <typename KVT>
 cudaError_t launch_ptc(cudaStream_t s, const AttnParams& p, uint32_t T) {
   dim3 grid((T + kPM - 1) / kPM, p.qH);
   switch (p.d) {
-    case 64: attn_prefill_tc_kernel<KVT, 64><<<grid, kPThreads, 0, s>>>(p, T); break;
-    case 128: attn_prefill_tc_kernel<KVT, 128><<<grid, kPThreads, 0, s>>>(p, T); break;
+    case 64: return launch_pdl(attn_prefill_tc_kernel<KVT, 64>, grid, dim3(kPThreads), 0, s, prefill_pdl(), p, T);
+    case 128: return launch_pdl(attn_prefill_tc_kernel<KVT, 128>, grid, dim3(kPThreads), 0, s, prefill_pdl(), p, T);
     default: return cudaErrorInvalidValue;
   }
-  return cudaGetLastError();
 }
 
 }  // namespace

@@ -19,6 +19,7 @@
 
 #include "common.cuh"
 #include "gemm_tc.h"
+#include "kernels.h"
 
 #include <stdlib.h>
 
@@ -199,6 +200,8 @@ __device__ __forceinline__ void partial_cols(float* part, uint32_t m, uint32_t n
 // Second kernel of a split GEMM: one thread per column pair adds the partials in split order and applies the epilogue.
 __global__ void __launch_bounds__(256) gemm_finish_kernel(const float* __restrict__ part, uint32_t M, uint32_t N, uint32_t Z,
                                                           const GemmEpilogue ep) {
+  pdl_launch_dependents();
+  pdl_wait();  // the partial tiles come from the GEMM launched just before
   const uint32_t pairs = (N + 1) / 2;
   const size_t total = (size_t)M * pairs;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -259,6 +262,9 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_kernel(const __grid_cons
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
+  // barriers and tensor memory are set up; the operands (and the residual) come from the previous kernel
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -376,6 +382,9 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_persistent_kernel(const 
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
+  // barriers and tensor memory are set up; the operands (and the residual) come from the previous kernel
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -468,6 +477,8 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_persistent_kernel(const 
 __global__ void __launch_bounds__(256) rmsnorm_to_half_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                                               float eps, uint32_t H, __half* __restrict__ out) {
   __shared__ float red[8];
+  pdl_launch_dependents();
+  pdl_wait();
   const float* xr = x + (size_t)blockIdx.x * H;
   float ss = 0.f;
   for (uint32_t i = threadIdx.x; i < H; i += 256) ss = fmaf(xr[i], xr[i], ss);
@@ -484,6 +495,8 @@ __global__ void __launch_bounds__(256) rmsnorm_to_half_kernel(const float* __res
 
 __global__ void embed_rows_kernel(const __half* __restrict__ E, const uint32_t* __restrict__ tokens, uint32_t H,
                                   float* __restrict__ x) {
+  pdl_launch_dependents();
+  pdl_wait();
   const __half* row = E + (size_t)tokens[blockIdx.x] * H;
   float* o = x + (size_t)blockIdx.x * H;
   for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) o[i] = __half2float(row[i]);
@@ -562,13 +575,12 @@ cudaError_t launch_bn(cudaStream_t s, const __half* A, const __half* W, uint32_t
     attr_device = dev;
   }
   dim3 grid((N + BN - 1) / BN, (M + kBM - 1) / kBM, Z);
-  kern<<<grid, kGemmThreads, smem, s>>>(mapA, mapW, M, N, K, ep, err);
-  e = cudaGetLastError();
+  e = launch_pdl(kern, grid, dim3(kGemmThreads), smem, s, prefill_pdl(), mapA, mapW, M, N, K, ep, err);
   if (e != cudaSuccess || Z == 1) return e;
   const size_t pairs = (size_t)M * ((N + 1) / 2);
   const size_t want = (pairs + 255) / 256;
-  gemm_finish_kernel<<<(unsigned)(want < 1184 ? want : 1184), 256, 0, s>>>(ep.scratch, M, N, Z, ep);
-  return cudaGetLastError();
+  return launch_pdl(gemm_finish_kernel, dim3((unsigned)(want < 1184 ? want : 1184)), dim3(256), 0, s, prefill_pdl(),
+                    (const float*)ep.scratch, M, N, Z, ep);
 }
 
 cudaError_t launch_persistent(cudaStream_t s, const __half* A, const __half* W, uint32_t M, uint32_t N, uint32_t K,
@@ -585,8 +597,8 @@ cudaError_t launch_persistent(cudaStream_t s, const __half* A, const __half* W, 
     attr_device = dev;
   }
   const uint32_t tiles = ((M + kBM - 1) / kBM) * ((N + kPBN - 1) / kPBN);
-  gemm_tc_persistent_kernel<<<tiles < 148 ? tiles : 148, kGemmThreads, PSmem::kTotal, s>>>(mapA, mapW, M, N, K, ep, err);
-  return cudaGetLastError();
+  return launch_pdl(gemm_tc_persistent_kernel, dim3(tiles < 148 ? tiles : 148), dim3(kGemmThreads), PSmem::kTotal, s,
+                    prefill_pdl(), mapA, mapW, M, N, K, ep, err);
 }
 
 }  // namespace
@@ -622,15 +634,18 @@ cudaError_t launch_gemm_tc(cudaStream_t s, const __half* A, const __half* W, uin
   return launch_bn<32, 8>(s, A, W, M, N, K, ep, err);
 }
 
+bool prefill_pdl() {
+  static const bool on = [] { const char* v = getenv("NFAI_PREFILL_PDL"); return !(v && atoi(v) == 0); }();
+  return on;
+}
+
 cudaError_t launch_rmsnorm_to_half(cudaStream_t s, const float* x, const float* gain, float eps, uint32_t M, uint32_t H,
                                    __half* out) {
-  rmsnorm_to_half_kernel<<<M, 256, 0, s>>>(x, gain, eps, H, out);
-  return cudaGetLastError();
+  return launch_pdl(rmsnorm_to_half_kernel, dim3(M), dim3(256), 0, s, prefill_pdl(), x, gain, eps, H, out);
 }
 
 cudaError_t launch_embed_rows(cudaStream_t s, const __half* E, const uint32_t* tokens, uint32_t M, uint32_t H, float* x) {
-  embed_rows_kernel<<<M, 256, 0, s>>>(E, tokens, H, x);
-  return cudaGetLastError();
+  return launch_pdl(embed_rows_kernel, dim3(M), dim3(256), 0, s, prefill_pdl(), E, tokens, H, x);
 }
 
 cudaError_t launch_float_to_half(cudaStream_t s, const float* in, __half* out, size_t n) {

@@ -15,6 +15,27 @@ inline cudaError_t prefer_max_shared(Kern kernel) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
 }
 
+// Launch with programmatic stream serialisation: the kernel may be scheduled while its predecessor in the stream is
+// still running; it must execute griddepcontrol.wait (pdl_wait) before it touches anything the predecessor wrote.
+// `pdl` = false gives a plain launch (the wait is then a no-op).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+// Prompt-path kernels overlap their launch and set-up with the predecessor's tail unless NFAI_PREFILL_PDL=0.
+bool prefill_pdl();
+
 // Device-resident state of one model: the graph's kernels read and advance it so that one captured graph
 // serves every position.
 struct StepState {
