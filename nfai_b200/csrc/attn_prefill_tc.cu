@@ -1,14 +1,15 @@
 // Causal attention over a chunk of prompt tokens on the tensor cores (flash-attention forward, one pass over K/V).
 //
 // The token-at-a-time prompt kernel (attn_prefill_kernel in attn.cu) re-reads the whole prefix of K and V for every
-// token: at 2 048 prompt tokens that is 80 % of the prompt time. Here a CTA owns 64 consecutive tokens of one
-// query head and walks the prefix once in tiles of 64 positions:
+// token: at 2 048 prompt tokens that is 80 % of the prompt time. Here a CTA owns 128 consecutive tokens of one
+// query head (8 warps x 16 rows) and walks the prefix once in tiles of 64 positions:
 //   S = Q K^T   (mma.sync m16n8k16, float16 operands, float32 accumulators; Q fragments stay in registers,
 //                pre-multiplied by 1/sqrt(d) * log2(e) so every exponential is one ex2)
 //   online softmax on the accumulator fragments (running max and sum per token row, quad shuffles)
 //   O += P V    (the S accumulators are re-packed as the A operand; V is read transposed with ldmatrix.trans)
-// K and V tiles are staged in shared memory (rows padded by 16 bytes: conflict-free ldmatrix), converted to
-// float16 on the way when the cache is float32. Each of the 4 warps owns 16 token rows.
+// K and V tiles are staged in shared memory (rows padded by 16 bytes: conflict-free ldmatrix) in two buffers: tile
+// i + 1 is copied with cp.async (16 bytes per copy, zero-filled past the range) while tile i is multiplied; a float32
+// cache is converted to float16 on the way in with plain loads instead.
 // Token t of the chunk sits at position p0 + t and attends to positions 0 .. p0 + t (causal); rows past the
 // chunk and positions past the last token are masked with -inf, and V rows past the range are zero-filled so that
 // a zero weight never meets a non-finite stale value.
@@ -25,9 +26,15 @@ namespace nfai {
 
 namespace {
 
-constexpr int kPM = 64;       // tokens per CTA
+constexpr int kPM = 128;      // tokens per CTA
 constexpr int kPN = 64;       // positions per K/V tile
-constexpr int kPThreads = 128;
+constexpr int kPThreads = 256;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
 __device__ __forceinline__ float p_ex2(float x) {
   float y;
@@ -53,7 +60,7 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint3
                : "r"(addr));
 }
 
-// eight consecutive cache elements of one row -> eight halves
+// eight consecutive float32 cache elements of one row -> eight halves (a float16 cache is copied with cp.async)
 __device__ __forceinline__ uint4 load8_as_half(const __half* p) { return *reinterpret_cast<const uint4*>(p); }
 __device__ __forceinline__ uint4 load8_as_half(const float* p) {
   const float4 a = *reinterpret_cast<const float4*>(p);
@@ -67,10 +74,12 @@ __device__ __forceinline__ uint4 load8_as_half(const float* p) {
 }
 
 template <typename KVT, int D>
-__global__ void __launch_bounds__(kPThreads) attn_prefill_tc_kernel(const AttnParams p, const uint32_t T) {
+__global__ void __launch_bounds__(kPThreads, D == 64 ? 2 : 1) attn_prefill_tc_kernel(const AttnParams p, const uint32_t T) {
   constexpr int LD = D + 8;  // shared-memory row stride in halves (16 bytes of padding)
-  __shared__ __align__(16) __half Ks[kPN * LD];
-  __shared__ __align__(16) __half Vs[kPN * LD];
+  constexpr int kTile = kPN * LD;  // halves of one K (or V) tile
+  extern __shared__ __align__(16) unsigned char ptc_smem[];
+  __half* const Ks = reinterpret_cast<__half*>(ptc_smem);  // [2][kTile]
+  __half* const Vs = Ks + 2 * kTile;                        // [2][kTile]
   pdl_launch_dependents();
   pdl_wait();  // q and the chunk's cache rows come from the QKV GEMM launched just before
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -110,34 +119,53 @@ __global__ void __launch_bounds__(kPThreads) attn_prefill_tc_kernel(const AttnPa
 
   const KVT* kbase = reinterpret_cast<const KVT*>(p.kcache) + (size_t)g * D;
   const KVT* vbase = reinterpret_cast<const KVT*>(p.vcache) + (size_t)g * D;
-  const uint32_t ks_s = (uint32_t)__cvta_generic_to_shared(Ks), vs_s = (uint32_t)__cvta_generic_to_shared(Vs);
+  const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(Ks), vs_base = (uint32_t)__cvta_generic_to_shared(Vs);
   // ldmatrix row addresses of this lane (see the operand layouts in the file header)
   const int lm = lane >> 3, lr = lane & 7;
   const uint32_t k_lane_off = (uint32_t)(((lm >> 1) * 8 + lr) * LD + (lm & 1) * 8) * 2;   // K: pair of position tiles
   const uint32_t v_lane_off = (uint32_t)(((lm & 1) * 8 + lr) * LD + (lm >> 1) * 8) * 2;   // V: pair of dim tiles
 
-  for (uint32_t n0 = 0; n0 < kv_end; n0 += kPN) {
-    __syncthreads();  // the previous tile has been consumed by every warp
-    constexpr int CPR = D / 8;  // 16-byte chunks per row
+  // copy (or convert) the K and V rows of tile `tile` into buffer `buf`
+  constexpr int CPR = D / 8;  // 16-byte chunks per row
+  auto issue = [&](int buf, uint32_t tile) {
+    const uint32_t n0 = tile * kPN;
 #pragma unroll
     for (int i = 0; i < kPN * CPR / kPThreads; ++i) {
       const int c = tid + i * kPThreads;
       const int r = c / CPR, c8 = (c % CPR) * 8;
       const uint32_t pos = n0 + r;
-      uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-      if (pos < kv_end) {
-        kv = load8_as_half(kbase + (size_t)pos * kvDim + c8);
-        vv = load8_as_half(vbase + (size_t)pos * kvDim + c8);
+      const bool in = pos < kv_end;
+      const size_t row = (size_t)(in ? pos : 0u) * kvDim + c8;  // a valid address even when nothing is copied
+      __half* kd = Ks + buf * kTile + r * LD + c8;
+      __half* vd = Vs + buf * kTile + r * LD + c8;
+      if constexpr (sizeof(KVT) == 2) {
+        cp_async16((uint32_t)__cvta_generic_to_shared(kd), kbase + row, in ? 16u : 0u);
+        cp_async16((uint32_t)__cvta_generic_to_shared(vd), vbase + row, in ? 16u : 0u);
+      } else {
+        uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+        if (in) {
+          kv = load8_as_half(kbase + row);
+          vv = load8_as_half(vbase + row);
+        }
+        *reinterpret_cast<uint4*>(kd) = kv;
+        *reinterpret_cast<uint4*>(vd) = vv;
       }
-      *reinterpret_cast<uint4*>(Ks + r * LD + c8) = kv;
-      *reinterpret_cast<uint4*>(Vs + r * LD + c8) = vv;
     }
-    __syncthreads();
-    // a warp whose rows all lie before this tile's first position has nothing to add (causal), but it must keep
+  };
+  const uint32_t ntiles = (kv_end + kPN - 1) / kPN;
+  issue(0, 0);
+  cp_async_commit();
+  for (uint32_t it = 0; it < ntiles; ++it) {
+    const uint32_t n0 = it * kPN;
+    if (it + 1 < ntiles) issue((int)((it + 1) & 1), it + 1);  // into the buffer every warp left at the end of iteration it - 1
+    cp_async_commit();                                         // (an empty group keeps the count uniform)
+    cp_async_wait_all_but_one();                               // this thread's copies of tile it have landed
+    __syncthreads();                                           // ... and everybody else's
+    const uint32_t ks_s = ks_base + (it & 1) * (uint32_t)(kTile * 2), vs_s = vs_base + (it & 1) * (uint32_t)(kTile * 2);
+    // a warp whose rows all lie before this tile's first position has nothing to add (causal), but it keeps
     // taking part in the block barriers
     const uint32_t warp_last_pos = p0 + blockIdx.x * kPM + warp * 16 + 15;
-    if (n0 > warp_last_pos) continue;
-
+    if (n0 <= warp_last_pos) {
     // ---- S = Q K^T : 16 rows x 64 positions per warp
     float s[kPN / 8][4];
 #pragma unroll
@@ -212,6 +240,8 @@ __global__ void __launch_bounds__(kPThreads) attn_prefill_tc_kernel(const AttnPa
         mma_16816(o[j + 1], pf[kk], b2, b3);
       }
     }
+    }  // tile visible to this warp
+    __syncthreads();  // every warp has left this buffer: the next iteration refills it
   }
   // ---- normalise and store (float16: the A operand of the output projection)
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
@@ -232,12 +262,27 @@ __global__ void __launch_bounds__(kPThreads) attn_prefill_tc_kernel(const AttnPa
   }
 }
 
+template <typename KVT, int D>
+cudaError_t launch_ptc_d(cudaStream_t s, const AttnParams& p, uint32_t T) {
+  constexpr size_t smem = (size_t)4 * kPN * (D + 8) * 2;  // two buffers of a K and a V tile
+  static thread_local int attr_device = -1;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (attr_device != dev) {
+    e = cudaFuncSetAttribute(attn_prefill_tc_kernel<KVT, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr_device = dev;
+  }
+  dim3 grid((T + kPM - 1) / kPM, p.qH);
+  return launch_pdl(attn_prefill_tc_kernel<KVT, D>, grid, dim3(kPThreads), smem, s, prefill_pdl(), p, T);
+}
+
 template <typename KVT>
 cudaError_t launch_ptc(cudaStream_t s, const AttnParams& p, uint32_t T) {
-  dim3 grid((T + kPM - 1) / kPM, p.qH);
   switch (p.d) {
-    case 64: return launch_pdl(attn_prefill_tc_kernel<KVT, 64>, grid, dim3(kPThreads), 0, s, prefill_pdl(), p, T);
-    case 128: return launch_pdl(attn_prefill_tc_kernel<KVT, 128>, grid, dim3(kPThreads), 0, s, prefill_pdl(), p, T);
+    case 64: return launch_ptc_d<KVT, 64>(s, p, T);
+    case 128: return launch_ptc_d<KVT, 128>(s, p, T);
     default: return cudaErrorInvalidValue;
   }
 }
