@@ -34,7 +34,7 @@ if ROOT not in sys.path:
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture
 # summarised in profiles/gemv_decode_llama1b_f16_ncu.md (configs[1], one GPU)
-NCU_TRAFFIC_BYTES = {("c1", 1): 67152128 + 350464}
+NCU_TRAFFIC_BYTES = {("c1", 1): 67155200 + 453376}
 PROMPT_LEN = 128
 
 
