@@ -41,6 +41,13 @@ internal static unsafe partial class Native
     [DllImport(Lib)] internal static extern int nfai_decode_greedy(IntPtr model, uint firstToken, int nSteps, uint* outTokens, float* elapsedMs);
     [DllImport(Lib)] internal static extern int nfai_sample_top_p(IntPtr model, float temperature, float topP, int topK, float u, out uint token);
     [DllImport(Lib)] internal static extern int nfai_op_sample_top_p(IntPtr ctx, IntPtr logits, uint V, float temperature, float topP, int topK, float u, IntPtr tokenOut);
+    // host-side tokenizer (no GPU work): token / merge byte strings as arrays of pointers + lengths
+    [DllImport(Lib)] internal static extern int nfai_tokenizer_create(IntPtr[] tokens, uint[] tokenLens, uint nTokens, IntPtr[] merges, uint[] mergeLens, uint nMerges, uint bosId, uint eosId, out IntPtr tokenizer);
+    [DllImport(Lib)] internal static extern void nfai_tokenizer_destroy(IntPtr tokenizer);
+    [DllImport(Lib)] internal static extern IntPtr nfai_tokenizer_last_error(IntPtr tokenizer);
+    [DllImport(Lib)] internal static extern int nfai_tokenizer_encode(IntPtr tokenizer, byte[] textUtf8, nuint textLen, uint[] idsOut, nuint cap, out nuint n);
+    [DllImport(Lib)] internal static extern int nfai_tokenizer_encode_chat(IntPtr tokenizer, byte[] promptUtf8, nuint promptLen, int addBos, uint[] idsOut, nuint cap, out nuint n);
+    [DllImport(Lib)] internal static extern int nfai_tokenizer_decode(IntPtr tokenizer, uint[] ids, nuint n, byte[] textOut, nuint cap, out nuint nOut);
     [DllImport(Lib)] internal static extern int nfai_position(IntPtr model, out uint pos);
     [DllImport(Lib)] internal static extern int nfai_reset(IntPtr model);
     [DllImport(Lib)] internal static extern int nfai_set_position(IntPtr model, uint pos);

@@ -313,6 +313,28 @@ int nfai_op_lm_head(nfai_ctx* ctx, const void* W, int dtype, const float* x, con
 int nfai_op_sample_top_p(nfai_ctx* c, const float* logits, uint32_t V, float temperature, float top_p, int top_k, float u,
                          uint32_t* token_out);
 
+/* ---- tokenizer (host side; no GPU work) ---------------------------------------------------------------------
+ * Byte-pair tokenizer with the observable behaviour of NFAI.Models.Llama3/Tokenizer.cs and a (left, right) -> rank
+ * hash map in place of its scan over the whole merges list for every adjacent pair (Tokenizer.cs:130-166).
+ * tokens[i] / token_lens[i]: the bytes of vocabulary entry i (tokenizer.ggml.tokens); merges[k]: "left right"
+ * (tokenizer.ggml.merges). Not thread-safe per handle. */
+typedef struct nfai_tokenizer nfai_tokenizer;
+/* replaces: Tokenizer(Dictionary<string, object> metadata) (Tokenizer.cs:16-58) */
+int nfai_tokenizer_create(const char* const* tokens, const uint32_t* token_lens, uint32_t n_tokens, const char* const* merges,
+                          const uint32_t* merge_lens, uint32_t n_merges, uint32_t bos_id, uint32_t eos_id,
+                          nfai_tokenizer** out);
+void nfai_tokenizer_destroy(nfai_tokenizer* t);
+const char* nfai_tokenizer_last_error(const nfai_tokenizer* t);
+/* UTF-8 text holding special tokens <|...|>: each special token, then the byte-pair encoding of the text behind it;
+ * text in front of the first special token is dropped, as the reference does (Tokenizer.cs:93-180).
+ * *n_out = number of ids (also when cap is too small: NFAI_ERR_ARG, call again with a larger buffer). */
+int nfai_tokenizer_encode(nfai_tokenizer* t, const char* text, size_t text_len, uint32_t* ids_out, size_t cap, size_t* n_out);
+/* replaces: Tokenizer.Tokenize(prompt, addBos) (Tokenizer.cs:68-182): the chat template around the user prompt. */
+int nfai_tokenizer_encode_chat(nfai_tokenizer* t, const char* prompt, size_t prompt_len, int add_bos, uint32_t* ids_out, size_t cap,
+                               size_t* n_out);
+/* replaces: Tokenizer.Detokenize (Tokenizer.cs:432-462): concatenated token bytes, U+0120 -> ' ', U+010A -> '\n'. */
+int nfai_tokenizer_decode(nfai_tokenizer* t, const uint32_t* ids, size_t n, char* text_out, size_t cap, size_t* n_out);
+
 #ifdef __cplusplus
 }
 #endif

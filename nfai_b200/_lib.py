@@ -62,6 +62,12 @@ SIGNATURES = {
     "nfai_decode_greedy": (_i, [_vp, _u32, _i, C.POINTER(_u32), C.POINTER(_f)]),
     "nfai_sample_top_p": (_i, [_vp, _f, _f, _i, _f, C.POINTER(_u32)]),
     "nfai_op_sample_top_p": (_i, [_vp, _vp, _u32, _f, _f, _i, _f, _vp]),
+    "nfai_tokenizer_create": (_i, [_vp, _vp, _u32, _vp, _vp, _u32, _u32, _u32, _pp]),
+    "nfai_tokenizer_destroy": (None, [_vp]),
+    "nfai_tokenizer_last_error": (C.c_char_p, [_vp]),
+    "nfai_tokenizer_encode": (_i, [_vp, C.c_char_p, _sz, _vp, _sz, C.POINTER(_sz)]),
+    "nfai_tokenizer_encode_chat": (_i, [_vp, C.c_char_p, _sz, _i, _vp, _sz, C.POINTER(_sz)]),
+    "nfai_tokenizer_decode": (_i, [_vp, _vp, _sz, _vp, _sz, C.POINTER(_sz)]),
     "nfai_position": (_i, [_vp, C.POINTER(_u32)]),
     "nfai_reset": (_i, [_vp]),
     "nfai_read_kv": (_i, [_vp, _u32, _u32, C.POINTER(_f), C.POINTER(_f)]),

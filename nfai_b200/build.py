@@ -21,7 +21,7 @@ LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libnfai_cuda.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
-SOURCES = ["api.cu", "gemv.cu", "gemv_ring.cu", "megastep.cu", "fused_ring.cu", "gemm_tc.cu", "attn.cu", "attn_ring.cu", "attn_prefill_tc.cu", "attn_static.cu", "misc.cu", "tp.cu", "gguf_loader.cu", "sample.cu"]
+SOURCES = ["api.cu", "gemv.cu", "gemv_ring.cu", "megastep.cu", "fused_ring.cu", "gemm_tc.cu", "attn.cu", "attn_ring.cu", "attn_prefill_tc.cu", "attn_static.cu", "misc.cu", "tp.cu", "gguf_loader.cu", "sample.cu", "tokenizer.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -51,7 +51,7 @@ def _deps_mtime() -> float:
     t = 0.0
     for root in (CSRC, INCLUDE):
         for f in os.listdir(root):
-            if f.endswith((".cu", ".cuh", ".h")):
+            if f.endswith((".cu", ".cpp", ".cuh", ".h")):
                 t = max(t, os.path.getmtime(os.path.join(root, f)))
     return t
 
@@ -71,7 +71,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                    if f.endswith((".cuh", ".h")))
 
     def compile_one(src: str) -> str:
-        obj = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
+        obj = os.path.join(OBJ_DIR, os.path.splitext(src)[0] + ".o")
         srcp = os.path.join(CSRC, src)
         if not force and os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(srcp), header_t):
             return obj

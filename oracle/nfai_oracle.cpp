@@ -542,3 +542,39 @@ extern "C" uint32_t orc_sample_top_p(const float* logits, uint64_t V, float temp
   }
   return idx.back();
 }
+
+// ---- byte-pair merge loop of the reference tokenizer, literally (NFAI.Models.Llama3/Tokenizer.cs:130-166) -----
+// For every adjacent pair of parts the whole merges list is scanned from the front until an entry equals the pair;
+// the pair with the lowest entry index wins (the leftmost among equals), one merge is applied, and the scan starts
+// over. parts / merges arrive as concatenated bytes with offset arrays (n + 1 entries; merges as 2 m + 1: left_0,
+// right_0, left_1, ...). Writes the offsets of the merged parts (the bytes themselves do not move) and returns their
+// number. Used to time the reference's algorithm in compiled code and to cross-check the Python restatement.
+extern "C" uint32_t orc_bpe_merge_scan(const uint8_t* part_bytes, const uint32_t* part_off, uint32_t n_parts,
+                                       const uint8_t* merge_bytes, const uint64_t* merge_off, uint32_t n_merges,
+                                       uint32_t* out_off) {
+  std::vector<std::pair<uint32_t, uint32_t>> parts;  // [begin, end) into part_bytes; merged parts stay contiguous
+  for (uint32_t i = 0; i < n_parts; ++i) parts.push_back({part_off[i], part_off[i + 1]});
+  auto equals = [&](const std::pair<uint32_t, uint32_t>& p, uint64_t mb, uint64_t me) {
+    return (uint64_t)(p.second - p.first) == me - mb && memcmp(part_bytes + p.first, merge_bytes + mb, me - mb) == 0;
+  };
+  while (true) {
+    long best_merge = -1, best_first = -1;
+    for (size_t j = 0; j + 1 < parts.size(); ++j) {
+      for (uint32_t k = 0; k < n_merges; ++k) {
+        if (equals(parts[j], merge_off[2 * k], merge_off[2 * k + 1]) && equals(parts[j + 1], merge_off[2 * k + 1], merge_off[2 * k + 2])) {
+          if (best_merge == -1 || (long)k < best_merge) {
+            best_merge = (long)k;
+            best_first = (long)j;
+          }
+          break;
+        }
+      }
+    }
+    if (best_merge == -1) break;
+    parts[best_first].second = parts[best_first + 1].second;
+    parts.erase(parts.begin() + best_first + 1);
+  }
+  for (size_t i = 0; i < parts.size(); ++i) out_off[i] = parts[i].first;
+  out_off[parts.size()] = parts.empty() ? 0 : parts.back().second;
+  return (uint32_t)parts.size();
+}

@@ -103,7 +103,28 @@ def make_sampling():
     print("sampling cases:", len(rows))
 
 
+# Tokenizer: the oracle's ids for the chat-templated form of a few texts over the synthetic vocabulary of
+# tests/tok_util.py.
+TOKENIZER_TEXTS = ["The quick brown fox jumps over a lazy dog.", "it's 12345 tokens,  isn't it?\n\nYes: naïve café!",
+                   "tab\tand\r\nwindows lines", "привет мир 日本語 \U0001F600"]
+
+
+def make_tokenizer():
+    from oracle.tokenizer_oracle import OracleTokenizer
+    from tests import tok_util
+    md = tok_util.metadata()
+    ref = OracleTokenizer(md["tokenizer.ggml.tokens"], md["tokenizer.ggml.merges"], 0, 1)
+    ids, offs = [], [0]
+    for t in TOKENIZER_TEXTS:
+        ids += ref.tokenize(t)
+        offs.append(len(ids))
+    np.savez_compressed(os.path.join(HERE, "tokenizer.npz"), texts=np.frombuffer("\x00".join(TOKENIZER_TEXTS).encode("utf-8"), np.uint8),
+                        ids=np.array(ids, np.uint32), offsets=np.array(offs, np.int64))
+    print("tokenizer cases:", len(TOKENIZER_TEXTS), "ids:", len(ids))
+
+
 if __name__ == "__main__":
     for k in CASES:
         make(k)
     make_sampling()
+    make_tokenizer()
