@@ -157,9 +157,16 @@ class Parser:
 
     def __init__(self, factories):
         self.factories = list(factories)
+        self.Tokenizer = None  # Parser.cs:13: set by parse() when the file carries a vocabulary
 
     def parse(self, options):
         meta, tensors = read_gguf(options.GGUFPath)
+        if "tokenizer.ggml.tokens" in meta and "tokenizer.ggml.bos_token_id" in meta:
+            from .tokenizer import Tokenizer
+            md = dict(meta)
+            md.setdefault("tokenizer.ggml.merges", [])
+            md.setdefault("tokenizer.ggml.eos_token_id", md["tokenizer.ggml.bos_token_id"])
+            self.Tokenizer = Tokenizer(md)
         for f in self.factories:
             model = f.try_create(meta, tensors, options)
             if model is not None:
