@@ -66,6 +66,18 @@ public sealed unsafe class CudaLlamaBackend : IDisposable
         return tok;
     }
 
+    // Multi-turn reuse: Prefill appends at the current position; a snapshot rewinds to an earlier point (for example
+    // right after a shared system prompt) without ingesting it again.
+    public IntPtr Snapshot()
+    {
+        Native.Check(Native.nfai_kv_snapshot_create(model, out IntPtr snap), ctx.Handle);
+        return snap;
+    }
+
+    public void Restore(IntPtr snapshot) => Native.Check(Native.nfai_kv_snapshot_restore(model, snapshot), ctx.Handle);
+
+    public static void FreeSnapshot(IntPtr snapshot) => Native.nfai_kv_snapshot_destroy(snapshot);
+
     public void Reset() => Native.Check(Native.nfai_reset(model), ctx.Handle);
 
     public void Dispose()

@@ -41,6 +41,10 @@ internal static unsafe partial class Native
     [DllImport(Lib)] internal static extern int nfai_decode_greedy(IntPtr model, uint firstToken, int nSteps, uint* outTokens, float* elapsedMs);
     [DllImport(Lib)] internal static extern int nfai_sample_top_p(IntPtr model, float temperature, float topP, int topK, float u, out uint token);
     [DllImport(Lib)] internal static extern int nfai_op_sample_top_p(IntPtr ctx, IntPtr logits, uint V, float temperature, float topP, int topK, float u, IntPtr tokenOut);
+    [DllImport(Lib)] internal static extern int nfai_kv_snapshot_create(IntPtr model, out IntPtr snapshot);
+    [DllImport(Lib)] internal static extern int nfai_kv_snapshot_restore(IntPtr model, IntPtr snapshot);
+    [DllImport(Lib)] internal static extern void nfai_kv_snapshot_destroy(IntPtr snapshot);
+    [DllImport(Lib)] internal static extern uint nfai_kv_snapshot_position(IntPtr snapshot);
     // host-side tokenizer (no GPU work): token / merge byte strings as arrays of pointers + lengths
     [DllImport(Lib)] internal static extern int nfai_tokenizer_create(IntPtr[] tokens, uint[] tokenLens, uint nTokens, IntPtr[] merges, uint[] mergeLens, uint nMerges, uint bosId, uint eosId, out IntPtr tokenizer);
     [DllImport(Lib)] internal static extern void nfai_tokenizer_destroy(IntPtr tokenizer);

@@ -313,6 +313,18 @@ int nfai_op_lm_head(nfai_ctx* ctx, const void* W, int dtype, const float* x, con
 int nfai_op_sample_top_p(nfai_ctx* c, const float* logits, uint32_t V, float temperature, float top_p, int top_k, float u,
                          uint32_t* token_out);
 
+/* ---- multi-turn reuse --------------------------------------------------------------------------------------
+ * nfai_prefill appends at the current position, so a second turn costs only its own tokens (the reference also keeps
+ * growing one cache across turns, LlamaModel.cs:17,101-102, but never rewinds and overflows silently). A snapshot
+ * holds the cache rows 0 .. position-1 of every layer, the last step's logits / arg-max and the position in device
+ * memory; restoring it rewinds the model to that point (a shared system prompt is ingested once). A snapshot belongs
+ * to the model it was taken from and must be destroyed before that model. No counterpart in the reference. */
+typedef struct nfai_kv_snapshot nfai_kv_snapshot;
+int nfai_kv_snapshot_create(nfai_model* m, nfai_kv_snapshot** out);
+int nfai_kv_snapshot_restore(nfai_model* m, const nfai_kv_snapshot* s);
+void nfai_kv_snapshot_destroy(nfai_kv_snapshot* s);
+uint32_t nfai_kv_snapshot_position(const nfai_kv_snapshot* s);
+
 /* ---- tokenizer (host side; no GPU work) ---------------------------------------------------------------------
  * Byte-pair tokenizer with the observable behaviour of NFAI.Models.Llama3/Tokenizer.cs and a (left, right) -> rank
  * hash map in place of its scan over the whole merges list for every adjacent pair (Tokenizer.cs:130-166).

@@ -62,6 +62,10 @@ SIGNATURES = {
     "nfai_decode_greedy": (_i, [_vp, _u32, _i, C.POINTER(_u32), C.POINTER(_f)]),
     "nfai_sample_top_p": (_i, [_vp, _f, _f, _i, _f, C.POINTER(_u32)]),
     "nfai_op_sample_top_p": (_i, [_vp, _vp, _u32, _f, _f, _i, _f, _vp]),
+    "nfai_kv_snapshot_create": (_i, [_vp, _pp]),
+    "nfai_kv_snapshot_restore": (_i, [_vp, _vp]),
+    "nfai_kv_snapshot_destroy": (None, [_vp]),
+    "nfai_kv_snapshot_position": (_u32, [_vp]),
     "nfai_tokenizer_create": (_i, [_vp, _vp, _u32, _vp, _vp, _u32, _u32, _u32, _pp]),
     "nfai_tokenizer_destroy": (None, [_vp]),
     "nfai_tokenizer_last_error": (C.c_char_p, [_vp]),

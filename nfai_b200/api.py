@@ -182,6 +182,12 @@ class LlamaModel:
                                            out.ctypes.data_as(C.POINTER(C.c_uint32)), C.byref(ms)), self.ctx.handle)
         return out, ms.value
 
+    def snapshot(self) -> "KvSnapshot":
+        """Copy of the cache rows, logits and position at this point (device memory); restore() rewinds to it."""
+        h = C.c_void_p()
+        check(self._lib.nfai_kv_snapshot_create(self.handle, C.byref(h)), self.ctx.handle)
+        return KvSnapshot(self, h)
+
     def sample_top_p(self, temperature: float = 0.5, top_p: float = 0.95, top_k: int = 40, u: float = 0.5) -> int:
         """SamplingUtils.TopP on the device over the last step's logits; `u` is the uniform draw."""
         tok = C.c_uint32()
@@ -274,6 +280,26 @@ class LlamaModel:
             self.Dispose()
         except Exception:
             pass
+
+
+class KvSnapshot:
+    """Handle of nfai_kv_snapshot_*: belongs to one model, close() it before the model."""
+
+    def __init__(self, model: "LlamaModel", handle):
+        self.model, self.handle = model, handle
+
+    @property
+    def position(self) -> int:
+        return int(self.model._lib.nfai_kv_snapshot_position(self.handle))
+
+    def restore(self, model: Optional["LlamaModel"] = None):
+        m = model or self.model
+        check(m._lib.nfai_kv_snapshot_restore(m.handle, self.handle), m.ctx.handle)
+
+    def close(self):
+        if self.handle:
+            self.model._lib.nfai_kv_snapshot_destroy(self.handle)
+            self.handle = None
 
 
 class LlamaModelFactory:

@@ -1296,6 +1296,96 @@ int nfai_set_position(nfai_model* m, uint32_t pos) {
 
 int nfai_reset(nfai_model* m) { return nfai_set_position(m, 0); }
 
+}  // extern "C"
+
+// A copy of everything a later turn needs to continue from this point: the cache rows of positions 0 .. pos-1 of every
+// layer, the logits and arg-max of the last step, and the position.
+struct nfai_kv_snapshot {
+  nfai_model* owner = nullptr;
+  int device = 0;
+  uint32_t pos = 0, cur_token = 0, last_argmax = 0;
+  char* dev = nullptr;
+  size_t row_bytes = 0;  // bytes of K (or V) of one layer: pos * kvDim * element size
+};
+
+extern "C" {
+
+int nfai_kv_snapshot_create(nfai_model* m, nfai_kv_snapshot** out) {
+  int rc = ready(m);
+  if (rc) return rc;
+  nfai_ctx* c = m->ctx;
+  if (!out) return fail(c, NFAI_ERR_ARG, "null output");
+  const nfai_hparams& hp = m->hp;
+  const size_t kvs = dtype_size(hp.kv_dtype);
+  StepState st;
+  if ((rc = check_state(m, &st))) return rc;
+  nfai_kv_snapshot* s = new nfai_kv_snapshot();
+  s->owner = m;
+  s->device = c->device;
+  s->pos = m->pos;
+  s->cur_token = st.cur_token;
+  s->last_argmax = st.last_argmax;
+  s->row_bytes = (size_t)m->pos * m->kvDimL * kvs;
+  const size_t total = 2 * (size_t)hp.L * s->row_bytes + (size_t)m->Vl * 4;
+  cudaError_t e = cudaMalloc((void**)&s->dev, total);
+  if (e != cudaSuccess) {
+    delete s;
+    return fail(c, NFAI_ERR_OOM, "cudaMalloc of %zu snapshot bytes: %s", total, cudaGetErrorString(e));
+  }
+  for (uint32_t l = 0; l < hp.L && e == cudaSuccess; ++l) {
+    const size_t lo = (size_t)l * kv_layer_elems(m) * kvs;
+    if (s->row_bytes) {
+      e = cudaMemcpyAsync(s->dev + (2 * (size_t)l) * s->row_bytes, (char*)m->kc + lo, s->row_bytes, cudaMemcpyDeviceToDevice, c->stream);
+      if (e == cudaSuccess)
+        e = cudaMemcpyAsync(s->dev + (2 * (size_t)l + 1) * s->row_bytes, (char*)m->vc + lo, s->row_bytes, cudaMemcpyDeviceToDevice, c->stream);
+    }
+  }
+  if (e == cudaSuccess)
+    e = cudaMemcpyAsync(s->dev + 2 * (size_t)hp.L * s->row_bytes, m->logits, (size_t)m->Vl * 4, cudaMemcpyDeviceToDevice, c->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+  if (e != cudaSuccess) {
+    cudaFree(s->dev);
+    delete s;
+    return fail(c, NFAI_ERR_CUDA, "snapshot copy: %s", cudaGetErrorString(e));
+  }
+  *out = s;
+  return NFAI_OK;
+}
+
+int nfai_kv_snapshot_restore(nfai_model* m, const nfai_kv_snapshot* s) {
+  int rc = ready(m);
+  if (rc) return rc;
+  nfai_ctx* c = m->ctx;
+  if (!s || s->owner != m) return fail(c, NFAI_ERR_ARG, "the snapshot was not taken from this model");
+  const nfai_hparams& hp = m->hp;
+  const size_t kvs = dtype_size(hp.kv_dtype);
+  CU(c, cudaSetDevice(c->device));
+  for (uint32_t l = 0; l < hp.L; ++l) {
+    const size_t lo = (size_t)l * kv_layer_elems(m) * kvs;
+    if (s->row_bytes) {
+      CU(c, cudaMemcpyAsync((char*)m->kc + lo, s->dev + (2 * (size_t)l) * s->row_bytes, s->row_bytes, cudaMemcpyDeviceToDevice, c->stream));
+      CU(c, cudaMemcpyAsync((char*)m->vc + lo, s->dev + (2 * (size_t)l + 1) * s->row_bytes, s->row_bytes, cudaMemcpyDeviceToDevice, c->stream));
+    }
+  }
+  CU(c, cudaMemcpyAsync(m->logits, s->dev + 2 * (size_t)hp.L * s->row_bytes, (size_t)m->Vl * 4, cudaMemcpyDeviceToDevice, c->stream));
+  if ((rc = set_state_word(m, offsetof(StepState, pos), s->pos, 3))) return rc;
+  if ((rc = set_state_word(m, offsetof(StepState, cur_token), s->cur_token, 4))) return rc;
+  if ((rc = set_state_word(m, offsetof(StepState, last_argmax), s->last_argmax, 5))) return rc;
+  if ((rc = set_state_word(m, offsetof(StepState, err), 0, 6))) return rc;
+  CU(c, cudaStreamSynchronize(c->stream));
+  m->pos = s->pos;
+  return NFAI_OK;
+}
+
+void nfai_kv_snapshot_destroy(nfai_kv_snapshot* s) {
+  if (!s) return;
+  cudaSetDevice(s->device);
+  if (s->dev) cudaFree(s->dev);
+  delete s;
+}
+
+uint32_t nfai_kv_snapshot_position(const nfai_kv_snapshot* s) { return s ? s->pos : 0; }
+
 static int kv_rw(nfai_model* m, uint32_t layer, uint32_t pos, float* k, float* v, const float* kin, const float* vin) {
   int rc = ready(m);
   if (rc) return rc;

@@ -347,3 +347,41 @@ def test_prompt_in_several_passes_equals_one_pass(monkeypatch):
     assert float(np.abs(out["64"][0] - out["2048"][0]).max()) <= 2e-3
     assert rel_err(out["64"][2][0], out["2048"][2][0]) <= 2e-3 and rel_err(out["64"][2][1], out["2048"][2][1]) <= 2e-3
     assert rel_err(out["64"][3], out["2048"][3]) <= 2e-3
+
+
+@pytest.mark.parametrize("key,kv", [("c0", "f32"), ("s3", "f16")])
+def test_snapshot_restore_rewinds_exactly(factory, key, kv):
+    """A later turn that starts from a restored snapshot sees bit-identical logits; the shared prefix is ingested once."""
+    cfg = synth.get_config(key)
+    toks = synth.prompt_ids(cfg, 14, 3)
+    m = make(cfg, 64, factory, kv_dtype=kv)
+    m.prefill(toks, want_logits=False)
+    snap = m.snapshot()
+    assert snap.position == m.position == 14
+    first = [m.decode(t)[0].copy() for t in (3, 5, 7)]
+    drawn = m.sample_top_p(u=0.25)
+    m.decode(9)                       # wander off: different tokens, more positions
+    m.prefill(synth.prompt_ids(cfg, 9, 5), want_logits=False)
+    snap.restore()
+    assert m.position == 14
+    again = [m.decode(t)[0].copy() for t in (3, 5, 7)]
+    for a, b in zip(first, again):
+        assert np.array_equal(a, b)
+    assert m.sample_top_p(u=0.25) == drawn
+    # rewinding also works after a reset, and the logits of the snapshot's own step come back
+    m.reset()
+    snap.restore()
+    assert m.sample_top_p(u=0.0) == m.sample_top_p(u=0.0)
+    assert [m.decode(t)[1] for t in (3, 5, 7)] == [oracle_argmax(x) for x in first]
+    # a snapshot belongs to its model
+    other = make(cfg, 64, factory, kv_dtype=kv)
+    with pytest.raises(NfaiError):
+        snap.restore(other)
+    snap.close()
+    other.Dispose()
+    m.Dispose()
+
+
+def oracle_argmax(v):
+    from oracle import oracle as O
+    return O.argmax(v)
