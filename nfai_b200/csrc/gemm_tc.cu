@@ -315,7 +315,13 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_kernel(const __grid_cons
       }
     }
   }
-  if (!ok && lane == 0 && err) atomicOr(err, 4u);
+  if (!ok) {
+    if (lane == 0 && err) atomicOr(err, 4u);
+    // tile copies of this CTA may still be in flight: give them a bounded time to land before shared memory and
+    // tensor memory are released
+    for (volatile uint32_t spin = 0; spin < (1u << 20); ++spin) {
+    }
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
@@ -465,7 +471,13 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_persistent_kernel(const 
       if (lane == 0) bar_arrive(tempty0 + 8 * acc);
     }
   }
-  if (!ok && lane == 0 && err) atomicOr(err, 4u);
+  if (!ok) {
+    if (lane == 0 && err) atomicOr(err, 4u);
+    // tile copies of this CTA may still be in flight: give them a bounded time to land before shared memory and
+    // tensor memory are released
+    for (volatile uint32_t spin = 0; spin < (1u << 20); ++spin) {
+    }
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
