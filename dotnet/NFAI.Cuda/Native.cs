@@ -41,6 +41,7 @@ internal static unsafe partial class Native
     [DllImport(Lib)] internal static extern int nfai_decode_greedy(IntPtr model, uint firstToken, int nSteps, uint* outTokens, float* elapsedMs);
     [DllImport(Lib)] internal static extern int nfai_sample_top_p(IntPtr model, float temperature, float topP, int topK, float u, out uint token);
     [DllImport(Lib)] internal static extern int nfai_op_sample_top_p(IntPtr ctx, IntPtr logits, uint V, float temperature, float topP, int topK, float u, IntPtr tokenOut);
+    [DllImport(Lib)] internal static extern int nfai_decode_sampled(IntPtr model, uint firstToken, int nSteps, float temperature, float topP, int topK, float[] u, uint[] tokensOut, out float elapsedMs);
     [DllImport(Lib)] internal static extern int nfai_kv_snapshot_create(IntPtr model, out IntPtr snapshot);
     [DllImport(Lib)] internal static extern int nfai_kv_snapshot_restore(IntPtr model, IntPtr snapshot);
     [DllImport(Lib)] internal static extern void nfai_kv_snapshot_destroy(IntPtr snapshot);

@@ -172,6 +172,13 @@ int nfai_decode_greedy(nfai_model* m, uint32_t first_token, int n_steps, uint32_
  *           LlamaModel.cs:128-130,165). */
 int nfai_sample_top_p(nfai_model* m, float temperature, float top_p, int top_k, float u, uint32_t* token_out);
 
+/* n_steps of decode with the draw of nfai_sample_top_p after every step, fed back on the device: logits, arg-max and
+ * the drawn tokens stay in device memory until the loop is over; u[i] is the uniform number of step i (the host draws
+ * them up front, e.g. from Random.Shared). The caller cuts the result at its end-of-sequence token.
+ * replaces: the sampling loop of LlamaModel.RunAsync (LlamaModel.cs:134-173) with SamplingUtils.TopP inside. */
+int nfai_decode_sampled(nfai_model* m, uint32_t first_token, int n_steps, float temperature, float top_p, int top_k,
+                        const float* u, uint32_t* out_tokens, float* elapsed_ms);
+
 /* Current position (number of tokens in the KV cache).
  * replaces: TransformerBlock.currentToken (TransformerBlock.cs:25,183) and
  *           MatrixMultiplyShader.currentCacheSize (NFAI.Vulkan.Shaders/MatrixMultiplyShader.cs:28). */

@@ -60,6 +60,7 @@ SIGNATURES = {
     "nfai_prefill": (_i, [_vp, C.POINTER(_u32), _i, C.POINTER(_f), C.POINTER(_u32)]),
     "nfai_decode": (_i, [_vp, _u32, C.POINTER(_f), C.POINTER(_u32)]),
     "nfai_decode_greedy": (_i, [_vp, _u32, _i, C.POINTER(_u32), C.POINTER(_f)]),
+    "nfai_decode_sampled": (_i, [_vp, _u32, _i, _f, _f, _i, _vp, _vp, C.POINTER(_f)]),
     "nfai_sample_top_p": (_i, [_vp, _f, _f, _i, _f, C.POINTER(_u32)]),
     "nfai_op_sample_top_p": (_i, [_vp, _vp, _u32, _f, _f, _i, _f, _vp]),
     "nfai_kv_snapshot_create": (_i, [_vp, _pp]),

@@ -182,6 +182,17 @@ class LlamaModel:
                                            out.ctypes.data_as(C.POINTER(C.c_uint32)), C.byref(ms)), self.ctx.handle)
         return out, ms.value
 
+    def decode_sampled(self, first_token: int, us: Sequence[float], temperature: float = 0.5, top_p: float = 0.95,
+                       top_k: int = 40) -> Tuple[np.ndarray, float]:
+        """len(us) steps with SamplingUtils.TopP after each, fed back on the device; returns (tokens, milliseconds)."""
+        u = np.ascontiguousarray(us, np.float32)
+        out = np.empty(len(u), np.uint32)
+        ms = C.c_float()
+        check(self._lib.nfai_decode_sampled(self.handle, int(first_token), len(u), temperature, top_p, top_k,
+                                            u.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p), C.byref(ms)),
+              self.ctx.handle)
+        return out, ms.value
+
     def snapshot(self) -> "KvSnapshot":
         """Copy of the cache rows, logits and position at this point (device memory); restore() rewinds to it."""
         h = C.c_void_p()

@@ -1278,6 +1278,42 @@ int nfai_sample_top_p(nfai_model* m, float temperature, float top_p, int top_k, 
   return NFAI_OK;
 }
 
+int nfai_decode_sampled(nfai_model* m, uint32_t first_token, int n_steps, float temperature, float top_p, int top_k,
+                        const float* u, uint32_t* out_tokens, float* elapsed_ms) {
+  int rc = ready(m);
+  if (rc) return rc;
+  nfai_ctx* c = m->ctx;
+  if (n_steps <= 0 || !u) return fail(c, NFAI_ERR_ARG, "n_steps must be positive and u must hold one number per step");
+  if (!(temperature > 0.f) || !(top_p > 0.f) || top_k < 1 || top_k > 64)
+    return fail(c, NFAI_ERR_ARG, "bad sampling parameters (temperature > 0, top_p > 0, 1 <= top_k <= 64)");
+  for (int i = 0; i < n_steps; ++i)
+    if (!(u[i] >= 0.f && u[i] < 1.f)) return fail(c, NFAI_ERR_ARG, "u[%d] is outside [0, 1)", i);
+  if (c->world != 1) return fail(c, NFAI_ERR_STATE, "on-device sampling needs the whole vocabulary on one GPU");
+  if ((uint64_t)m->pos + (uint64_t)n_steps > m->hp.ctx)
+    return fail(c, NFAI_ERR_CONTEXT_FULL, "%d steps from position %u exceed the KV-cache capacity %u", n_steps, m->pos, m->hp.ctx);
+  if (first_token >= m->hp.V) return fail(c, NFAI_ERR_ARG, "token id %u out of range (V = %u)", first_token, m->hp.V);
+  if ((rc = set_state_word(m, offsetof(StepState, cur_token), first_token, 0))) return rc;
+  if ((rc = set_state_word(m, offsetof(StepState, steps), 0, 2))) return rc;
+  CU(c, cudaEventRecord(c->ev0, c->stream));
+  for (int i = 0; i < n_steps; ++i) {
+    // the step leaves logits, arg-max and history[i] = arg-max; the sampler then puts the drawn token into history[i]
+    // and into cur_token, which the next step embeds -- nothing returns to the host inside the loop
+    if ((rc = run_step(m, true, false))) return rc;
+    CU(c, launch_sample_top_p(c->stream, m->logits, m->hp.V, &m->state->last_argmax, &m->state->cur_token, temperature, top_p,
+                              top_k, u[i], m->sample_scratch, m->history + i));
+  }
+  CU(c, cudaEventRecord(c->ev1, c->stream));
+  m->pos += (uint32_t)n_steps;
+  if ((rc = check_state(m, nullptr))) return rc;
+  if (elapsed_ms) CU(c, cudaEventElapsedTime(elapsed_ms, c->ev0, c->ev1));
+  std::vector<uint32_t> toks((size_t)n_steps);
+  CU(c, cudaMemcpy(toks.data(), m->history, (size_t)n_steps * 4, cudaMemcpyDeviceToHost));
+  for (int i = 0; i < n_steps; ++i)
+    if (toks[i] == 0xffffffffu) return fail(c, NFAI_ERR_STATE, "step %d: the logits buffer and the step's arg-max are out of step", i);
+  if (out_tokens) memcpy(out_tokens, toks.data(), (size_t)n_steps * 4);
+  return NFAI_OK;
+}
+
 int nfai_position(const nfai_model* m, uint32_t* pos) {
   if (!m || !pos) return fail(m ? m->ctx : nullptr, NFAI_ERR_ARG, "null argument");
   *pos = m->pos;

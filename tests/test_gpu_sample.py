@@ -120,3 +120,34 @@ def test_sampling_golden(cuda_ctx):
         V = int(V)
         logits = cache.setdefault(V, sample_logits(V))
         assert _sample(cuda_ctx, logits, float(T), float(p), int(k), float(np.float32(u))) == int(tok)
+
+
+def test_sampled_loop_on_the_device_equals_the_per_token_calls(oracle):
+    """nfai_decode_sampled: step + draw fed back on the device, against decode() + sample_top_p() per token."""
+    cfg = synth.get_config("c0")
+    factory = api.LlamaModelFactory(0)
+    a = api.create_synthetic_model(cfg, 64, factory=factory)
+    b = api.create_synthetic_model(cfg, 64, factory=factory)
+    prompt = synth.prompt_ids(cfg, 6, 2)
+    _, am = a.prefill(prompt)
+    b.prefill(prompt, want_logits=False)
+    us = np.random.default_rng(8).random(24, dtype=np.float32)
+    want, tok = [], am
+    for u in us:
+        logits, _ = a.decode(tok)
+        tok = a.sample_top_p(u=float(u))
+        if _margin(logits, 0.5, 0.95, 40, float(u)) >= 1e-4:
+            assert tok == oracle.sample_top_p(logits, u=float(u))
+        want.append(tok)
+    got, ms = b.decode_sampled(am, us)
+    assert list(got) == want and ms > 0
+    assert a.position == b.position == 6 + 24
+    # the loop leaves the model ready for the next call: same continuation on both
+    la, _ = a.decode(want[-1])
+    lb, _ = b.decode(want[-1])
+    assert np.array_equal(la, lb)
+    with pytest.raises(api.NfaiError):
+        b.decode_sampled(am, [1.5])
+    a.Dispose()
+    b.Dispose()
+    factory.Dispose()
