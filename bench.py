@@ -245,6 +245,17 @@ def run_ours(args, cfg):
     for name in ("ffn_gate_up", "ffn_down", "qkv_rope", "attn_out", "lm_head", "attention"):
         kms, kbytes = model.profile_kernel(name, 64 if name != "lm_head" else 16)
         kern[name] = {"us": kms * 1e3, "bytes": kbytes, "gbs": kbytes / (kms * 1e-3) / 1e9}
+    # ---- sampled decoding with the draw on the device (temperature 0.5, top-p 0.95, top-k 40 as in the reference)
+    sampled = None
+    if world == 1:
+        import numpy as np
+        model.set_position(PROMPT_LEN)
+        us = np.random.default_rng(args.seed + 7).random(K, dtype=np.float32)
+        model.decode_sampled(am, us[:min(W, K)])
+        model.set_position(PROMPT_LEN)
+        _, sms = model.decode_sampled(am, us)
+        sampled = {"value": K / (sms * 1e-3), "unit": "tok/s", "steps": K,
+                   "what": "decode step + top-p draw fed back on the device (nfai_decode_sampled)"}
     launches = model.step_launches()
     kv_bytes = 2 if model.kv_dtype == "f16" else 4
     first_pos = PROMPT_LEN + W
@@ -276,6 +287,7 @@ def run_ours(args, cfg):
         "step_roofline": {"bytes_per_token_per_gpu": step_bytes, "achieved_gbs": step_bytes / (ms / K * 1e-3) / 1e9,
                           "frac_of_8tbs": step_bytes / (ms / K * 1e-3) / 8e12,
                           "frac_of_measured": step_bytes / (ms / K * 1e-3) / 1e9 / peak},
+        "sampled": sampled,
         "kernels": kern,
         "clocks": clocks,
         "load_s": load_s, "prefill_tok_s": PROMPT_LEN / prefill_s,
