@@ -9,6 +9,8 @@
 //
 // Two kernels: every CTA takes a slice of the vocabulary, sums exp(scaled - max) in double and selects its own
 // top_k by repeated block arg-max; one CTA then merges the slices' candidates the same way and samples.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -220,6 +222,206 @@ __global__ void __launch_bounds__(1024) sample_argmax_kernel(const float* __rest
   }
 }
 
+// ---- fast path for large vocabularies: histogram cut instead of 2 x top_k rounds of block arg-max ---------------
+// Pass 1 sums exp(scaled - max) per CTA (as above) and counts the scaled logits in 128 bins of width 1/4 below the
+// maximum. The bin in which the count from the top reaches top_k bounds the top_k-th largest value from below, so
+// pass 2 keeps every element of that bin and the bins above it (typically a few dozen to a few hundred of 128 256).
+// Pass 3 (one CTA) ranks the kept elements by counting, in the reference's order (value descending, index ascending;
+// the order in which pass 2 appended them does not matter), and runs the same cumulative / renormalise / draw code.
+// More than kMaxCand kept elements (a nearly flat distribution) falls back, inside pass 3, to block arg-max rounds
+// over the whole vector.
+constexpr int kHistBins = 128;
+constexpr float kBinsPerUnit = 4.0f;
+constexpr int kMaxCand = 1024;
+
+__device__ __forceinline__ int hist_bin(float scaled, float mx) {
+  const float d = (mx - scaled) * kBinsPerUnit;  // >= 0 up to rounding
+  const int b = d <= 0.f ? 0 : (d >= (float)(kHistBins - 1) ? kHistBins - 1 : (int)d);
+  return b;
+}
+
+__global__ void __launch_bounds__(kST) sample_hist_kernel(const float* __restrict__ logits, uint32_t V, uint32_t slice,
+                                                         const uint32_t* __restrict__ argmax, float temperature,
+                                                         double* __restrict__ part_sum, uint32_t* __restrict__ ghist) {
+  __shared__ double dsum[kST / 32];
+  __shared__ uint32_t hist[kHistBins];
+  if (threadIdx.x < kHistBins) hist[threadIdx.x] = 0;
+  __syncthreads();
+  const uint32_t lo = blockIdx.x * slice;
+  const uint32_t am = *argmax;
+  const float mx = logits[am < V ? am : 0] / temperature;
+  double s = 0.0;
+#pragma unroll
+  for (int k = 0; k < kSPer; ++k) {
+    const uint32_t i = lo + k * kST + threadIdx.x;
+    if (k * kST + threadIdx.x < slice && i < V) {
+      const float v = logits[i] / temperature;
+      s += (double)expf(v - mx);
+      atomicAdd(&hist[hist_bin(v, mx)], 1u);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) dsum[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < kST / 32; ++w) t += dsum[w];
+    part_sum[blockIdx.x] = t;
+  }
+  if (threadIdx.x < kHistBins && hist[threadIdx.x]) atomicAdd(&ghist[threadIdx.x], hist[threadIdx.x]);
+}
+
+__global__ void __launch_bounds__(kST) sample_collect_kernel(const float* __restrict__ logits, uint32_t V, uint32_t slice,
+                                                            const uint32_t* __restrict__ argmax, float temperature, int top_k,
+                                                            const uint32_t* __restrict__ ghist, uint32_t* __restrict__ count,
+                                                            float* __restrict__ cand_val, uint32_t* __restrict__ cand_idx) {
+  __shared__ int cut;
+  if (threadIdx.x == 0) {
+    uint32_t c = 0;
+    int b = 0;
+    for (; b < kHistBins - 1; ++b) {
+      c += ghist[b];
+      if (c >= (uint32_t)top_k) break;
+    }
+    cut = b;  // every bin up to and including this one is kept
+  }
+  __syncthreads();
+  const int cutb = cut;
+  const uint32_t lo = blockIdx.x * slice;
+  const uint32_t am = *argmax;
+  const float mx = logits[am < V ? am : 0] / temperature;
+#pragma unroll
+  for (int k = 0; k < kSPer; ++k) {
+    const uint32_t i = lo + k * kST + threadIdx.x;
+    if (k * kST + threadIdx.x < slice && i < V) {
+      const float v = logits[i] / temperature;
+      if (hist_bin(v, mx) <= cutb) {
+        const uint32_t slot = atomicAdd(count, 1u);
+        if (slot < (uint32_t)kMaxCand) {
+          cand_val[slot] = v;
+          cand_idx[slot] = i;
+        }
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(1024) sample_pick_kernel(const float* __restrict__ logits, uint32_t V,
+                                                           const uint32_t* __restrict__ argmax, uint32_t* cur_token,
+                                                           float temperature, float top_p, int top_k, float u, int nslices,
+                                                           const double* __restrict__ part_sum, uint32_t* __restrict__ ghist,
+                                                           uint32_t* __restrict__ count, const float* __restrict__ cand_val,
+                                                           const uint32_t* __restrict__ cand_idx, uint32_t* __restrict__ token_out) {
+  __shared__ float sv[kMaxCand];
+  __shared__ uint32_t si[kMaxCand];
+  __shared__ Pick chosen[kMaxTopK];
+  __shared__ Pick sm[32];
+  __shared__ Pick bcast;
+  const uint32_t total = *count;
+  const int tid = threadIdx.x;
+  if (tid < kMaxTopK) chosen[tid] = Pick{0.f, 0xffffffffu};
+  __syncthreads();
+  if (total <= (uint32_t)kMaxCand) {
+    const int n = (int)total;
+    if (tid < n) {
+      sv[tid] = cand_val[tid];
+      si[tid] = cand_idx[tid];
+    }
+    __syncthreads();
+    if (tid < n) {
+      const float v = sv[tid];
+      const uint32_t i = si[tid];
+      int rank = 0;
+      for (int c = 0; c < n; ++c) rank += before(sv[c], si[c], v, i) ? 1 : 0;
+      if (rank < top_k) chosen[rank] = Pick{v, i};
+    }
+  } else {
+    // nearly flat distribution: top_k rounds of block arg-max over the whole vector
+    for (int r = 0; r < top_k; ++r) {
+      float bv = 0.f;
+      uint32_t bi = 0xffffffffu;
+      for (uint32_t c = tid; c < V; c += 1024) {
+        const float v = logits[c] / temperature;
+        if (r > 0) {
+          const Pick last = chosen[r - 1];
+          if (!before(last.v, last.i, v, c)) continue;
+        }
+        if (bi == 0xffffffffu || before(v, c, bv, bi)) {
+          bv = v;
+          bi = c;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi != 0xffffffffu && (bi == 0xffffffffu || before(ov, oi, bv, bi))) {
+          bv = ov;
+          bi = oi;
+        }
+      }
+      if ((tid & 31) == 0) sm[tid >> 5] = Pick{bv, bi};
+      __syncthreads();
+      if (tid < 32) {
+        Pick q = sm[tid];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, q.v, o);
+          const uint32_t oi = __shfl_xor_sync(0xffffffffu, q.i, o);
+          if (oi != 0xffffffffu && (q.i == 0xffffffffu || before(ov, oi, q.v, q.i))) {
+            q.v = ov;
+            q.i = oi;
+          }
+        }
+        if (tid == 0) bcast = q;
+      }
+      __syncthreads();
+      if (tid == 0) chosen[r] = bcast;
+      __syncthreads();
+    }
+  }
+  __syncthreads();
+  // the scratch counters go back to zero for the next call
+  if (tid < kHistBins) ghist[tid] = 0;
+  if (tid == 0) *count = 0;
+  if (tid == 0) {
+    double tot = 0.0;
+    for (int c = 0; c < nslices; ++c) tot += part_sum[c];
+    const float sumf = (float)tot;
+    const uint32_t am = *argmax;
+    const float mx = logits[am < V ? am : 0] / temperature;
+    if (am >= V || chosen[0].i == 0xffffffffu || chosen[0].v != mx) {  // the arg-max does not belong to these logits
+      *token_out = 0xffffffffu;
+      return;
+    }
+    float pr[kMaxTopK];
+    int n = 0;
+    float cumulative = 0.f;
+    for (int r = 0; r < top_k; ++r) {
+      if (chosen[r].i == 0xffffffffu) break;
+      const float p = __fdiv_rn(expf(chosen[r].v - mx), sumf);
+      cumulative += p;
+      pr[n++] = p;
+      if (cumulative >= top_p) break;
+    }
+    double t2 = 0.0;
+    for (int r = 0; r < n; ++r) t2 += (double)pr[r];
+    const float totalp = (float)t2;
+    uint32_t tok = chosen[n > 0 ? n - 1 : 0].i;
+    float running = 0.f;
+    for (int r = 0; r < n; ++r) {
+      running += __fdiv_rn(pr[r], totalp);
+      if (u < running) {
+        tok = chosen[r].i;
+        break;
+      }
+    }
+    *token_out = tok;
+    if (cur_token) *cur_token = tok;
+  }
+}
+
 }  // namespace
 
 size_t sample_scratch_bytes(uint32_t V, int* nslices_out) {
@@ -237,6 +439,25 @@ cudaError_t launch_sample_top_p(cudaStream_t s, const float* logits, uint32_t V,
   const uint32_t slice = (V + nslices - 1) / nslices;
   if (slice > (uint32_t)kSliceMax) return cudaErrorInvalidValue;
   double* part_sum = reinterpret_cast<double*>(scratch);
+  static const bool fast_ok = [] { const char* v = getenv("NFAI_SAMPLE_FAST"); return !(v && atoi(v) == 0); }();
+  if (fast_ok && nslices >= 148) {  // the scratch of >= 148 slices holds the histogram path's buffers
+    uint32_t* ghist = reinterpret_cast<uint32_t*>(part_sum + nslices);
+    uint32_t* count = ghist + kHistBins;
+    float* fval = reinterpret_cast<float*>(count + 4);
+    uint32_t* fidx = reinterpret_cast<uint32_t*>(fval + kMaxCand);
+    cudaError_t e = cudaMemsetAsync(ghist, 0, (kHistBins + 4) * sizeof(uint32_t), s);
+    if (e != cudaSuccess) return e;
+    if (!argmax) {
+      uint32_t* am = fidx + kMaxCand;
+      sample_argmax_kernel<<<1, 1024, 0, s>>>(logits, V, am);
+      argmax = am;
+    }
+    sample_hist_kernel<<<nslices, kST, 0, s>>>(logits, V, slice, argmax, temperature, part_sum, ghist);
+    sample_collect_kernel<<<nslices, kST, 0, s>>>(logits, V, slice, argmax, temperature, top_k, ghist, count, fval, fidx);
+    sample_pick_kernel<<<1, 1024, 0, s>>>(logits, V, argmax, cur_token, temperature, top_p, top_k, u, nslices, part_sum, ghist,
+                                          count, fval, fidx, token_out);
+    return cudaGetLastError();
+  }
   float* cand_val = reinterpret_cast<float*>(part_sum + nslices);
   uint32_t* cand_idx = reinterpret_cast<uint32_t*>(cand_val + (size_t)nslices * kMaxTopK);
   if (!argmax) {
