@@ -52,6 +52,7 @@ internal static unsafe partial class Native
     [DllImport(Lib)] internal static extern IntPtr nfai_tokenizer_last_error(IntPtr tokenizer);
     [DllImport(Lib)] internal static extern int nfai_tokenizer_encode(IntPtr tokenizer, byte[] textUtf8, nuint textLen, uint[] idsOut, nuint cap, out nuint n);
     [DllImport(Lib)] internal static extern int nfai_tokenizer_encode_chat(IntPtr tokenizer, byte[] promptUtf8, nuint promptLen, int addBos, uint[] idsOut, nuint cap, out nuint n);
+    [DllImport(Lib)] internal static extern int nfai_tokenizer_pretokenize(IntPtr tokenizer, byte[] textUtf8, nuint textLen, uint[] endsOut, nuint cap, out nuint n);
     [DllImport(Lib)] internal static extern int nfai_tokenizer_decode(IntPtr tokenizer, uint[] ids, nuint n, byte[] textOut, nuint cap, out nuint nOut);
     [DllImport(Lib)] internal static extern int nfai_position(IntPtr model, out uint pos);
     [DllImport(Lib)] internal static extern int nfai_reset(IntPtr model);

@@ -351,6 +351,9 @@ int nfai_tokenizer_encode(nfai_tokenizer* t, const char* text, size_t text_len, 
 /* replaces: Tokenizer.Tokenize(prompt, addBos) (Tokenizer.cs:68-182): the chat template around the user prompt. */
 int nfai_tokenizer_encode_chat(nfai_tokenizer* t, const char* prompt, size_t prompt_len, int add_bos, uint32_t* ids_out, size_t cap,
                                size_t* n_out);
+/* Tap for the parity tests: the end offsets (in UTF-16 code units) of the pieces the pre-tokenisation pattern
+ * (Tokenizer.cs:109-111) cuts `text` into. No counterpart in the reference. */
+int nfai_tokenizer_pretokenize(nfai_tokenizer* t, const char* text, size_t text_len, uint32_t* ends_out, size_t cap, size_t* n_out);
 /* replaces: Tokenizer.Detokenize (Tokenizer.cs:432-462): concatenated token bytes, U+0120 -> ' ', U+010A -> '\n'. */
 int nfai_tokenizer_decode(nfai_tokenizer* t, const uint32_t* ids, size_t n, char* text_out, size_t cap, size_t* n_out);
 

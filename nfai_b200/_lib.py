@@ -72,6 +72,7 @@ SIGNATURES = {
     "nfai_tokenizer_last_error": (C.c_char_p, [_vp]),
     "nfai_tokenizer_encode": (_i, [_vp, C.c_char_p, _sz, _vp, _sz, C.POINTER(_sz)]),
     "nfai_tokenizer_encode_chat": (_i, [_vp, C.c_char_p, _sz, _i, _vp, _sz, C.POINTER(_sz)]),
+    "nfai_tokenizer_pretokenize": (_i, [_vp, C.c_char_p, _sz, _vp, _sz, C.POINTER(_sz)]),
     "nfai_tokenizer_decode": (_i, [_vp, _vp, _sz, _vp, _sz, C.POINTER(_sz)]),
     "nfai_position": (_i, [_vp, C.POINTER(_u32)]),
     "nfai_reset": (_i, [_vp]),

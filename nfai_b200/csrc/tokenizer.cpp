@@ -315,6 +315,18 @@ int nfai_tokenizer_encode_chat(nfai_tokenizer* t, const char* prompt, size_t pro
   return copy_out(t, ids, ids_out, cap, n_out);
 }
 
+int nfai_tokenizer_pretokenize(nfai_tokenizer* t, const char* text, size_t text_len, uint32_t* ends_out, size_t cap, size_t* n_out) {
+  if (!t || (!text && text_len) || !n_out) return NFAI_ERR_ARG;
+  const std::vector<uint16_t> units = to_utf16(text ? text : "", text_len);
+  std::vector<uint32_t> ends;
+  size_t i = 0;
+  while (i < units.size()) {
+    i += match_at(units, i);
+    ends.push_back((uint32_t)i);
+  }
+  return copy_out(t, ends, ends_out, cap, n_out);
+}
+
 int nfai_tokenizer_decode(nfai_tokenizer* t, const uint32_t* ids, size_t n, char* text_out, size_t cap, size_t* n_out) {
   if (!t || (!ids && n) || !n_out) return NFAI_ERR_ARG;
   std::string bytes;

@@ -69,6 +69,11 @@ class Tokenizer:
         b = text.encode("utf-8")
         return self._ids(lambda buf, cap, n: self._lib.nfai_tokenizer_encode(self.handle, b, len(b), C.cast(buf, C.c_void_p), cap, n))
 
+    def pretokenize_ends(self, text: str) -> List[int]:
+        """End offsets (UTF-16 code units) of the pieces the pre-tokenisation pattern cuts `text` into (test tap)."""
+        b = text.encode("utf-8")
+        return self._ids(lambda buf, cap, n: self._lib.nfai_tokenizer_pretokenize(self.handle, b, len(b), C.cast(buf, C.c_void_p), cap, n))
+
     def tokenize(self, prompt: str, add_bos: bool = True) -> List[int]:
         """Tokenizer.Tokenize: the chat template around the user prompt (Tokenizer.cs:68-182)."""
         b = prompt.encode("utf-8")

@@ -144,3 +144,35 @@ def test_compiled_reference_scan_equals_the_python_restatement(pair):
     fast = OracleTokenizer(md["tokenizer.ggml.tokens"], md["tokenizer.ggml.merges"], 0, 1, compiled=True)
     for text in EDGE_CASES + [" ".join(tok_util._WORDS)]:
         assert _outcome(lambda: fast.tokenize(text)) == _outcome(lambda: ref.tokenize(text))
+
+
+def test_pretokenisation_matches_the_pattern_on_unicode_text(pair):
+    """The hand-written matcher against the pattern itself (third-party `regex` on UTF-16 code units) on random text
+    drawn from letters, numbers, marks, punctuation, symbols, separators and controls of many scripts."""
+    import unicodedata
+
+    from oracle.tokenizer_oracle import META, utf16_units
+    native, _, _ = pair
+    rng = np.random.default_rng(21)
+    pools = {}
+    for cp in list(range(0x20, 0x3000)) + list(range(0x3040, 0x3100)) + list(range(0x4E00, 0x4E80)) + list(range(0xAC00, 0xAC40)) + \
+            list(range(0xFF00, 0xFFEF)) + [0x09, 0x0A, 0x0B, 0x0C, 0x0D, 0x85, 0x1F600, 0x1F680, 0x10400, 0x1D7D8]:
+        if 0xD800 <= cp <= 0xDFFF:
+            continue
+        pools.setdefault(unicodedata.category(chr(cp))[0], []).append(chr(cp))
+    common = list(" \n\r\t'abcXYZ019.,!-")
+    checked = 0
+    for trial in range(600):
+        n = int(rng.integers(1, 40))
+        chars = []
+        for _ in range(n):
+            if rng.random() < 0.5:
+                chars.append(common[int(rng.integers(0, len(common)))])
+            else:
+                cat = list(pools)[int(rng.integers(0, len(pools)))]
+                chars.append(pools[cat][int(rng.integers(0, len(pools[cat])))])
+        text = "".join(chars)
+        want = [m.end() for m in META.finditer(utf16_units(text))]
+        assert native.pretokenize_ends(text) == want, repr(text)
+        checked += len(want)
+    assert checked > 5000
