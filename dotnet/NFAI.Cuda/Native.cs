@@ -33,6 +33,7 @@ internal static unsafe partial class Native
     [DllImport(Lib)] internal static extern int nfai_model_tensor_end(IntPtr model);
     [DllImport(Lib)] internal static extern int nfai_model_finalize(IntPtr model);
     [DllImport(Lib, CharSet = CharSet.Ansi)] internal static extern int nfai_model_load_gguf(IntPtr ctx, string path, uint kvCacheSize, int kvDType, out IntPtr model);
+    [DllImport(Lib, CharSet = CharSet.Ansi)] internal static extern int nfai_gguf_probe(string path, uint kvCacheSize, out NfaiHParams hp, byte* errOut, nuint errBytes);
     [DllImport(Lib)] internal static extern int nfai_model_get_hparams(IntPtr model, out NfaiHParams hp);
     [DllImport(Lib)] internal static extern int nfai_op_gemm_f16(IntPtr ctx, void* a, void* w, uint m, uint n, uint k, float* c);
     [DllImport(Lib)] internal static extern int nfai_model_destroy(IntPtr model);
@@ -62,8 +63,6 @@ internal static unsafe partial class Native
     [DllImport(Lib)] internal static extern int nfai_read_hidden(IntPtr model, uint layer, float* outHidden);
     [DllImport(Lib)] internal static extern int nfai_model_tune(IntPtr model, int which, int mode, int rowsPerWarp, int depth, int ctasPerSm);
     [DllImport(Lib)] internal static extern int nfai_model_set_prefetch(IntPtr model, ulong lookaheadBytes, ulong extraBytes, int mode);
-    [DllImport(Lib)] internal static extern int nfai_model_set_fused_step(IntPtr model, int enabled);
-    [DllImport(Lib)] internal static extern int nfai_model_trace(IntPtr model, ulong* nsOut, int capacity, out int count);
     [DllImport(Lib)] internal static extern int nfai_op_attn_decode_static(IntPtr ctx, float* q, void* kcache, void* vcache, int kvDType, uint seq, uint qH, uint kvH, uint d, float* outp);
     [DllImport(Lib)] internal static extern int nfai_profile_kernel(IntPtr model, int which, int iters, out float avgMs, out ulong bytesPerLaunch);
     [DllImport(Lib)] internal static extern int nfai_step_launches(IntPtr model, out int launches);

@@ -137,6 +137,14 @@ int nfai_model_finalize(nfai_model* m);
  *           (NFAI.Vulkan/VulkanBufferManager.cs:105-194) for hosts that want the native loader. */
 int nfai_model_load_gguf(nfai_ctx* ctx, const char* path, uint32_t kv_cache_size, int kv_dtype, nfai_model** out);
 
+/* Read only the header, metadata and tensor directory of a GGUF file and report the geometry nfai_model_load_gguf
+ * would create, with every size and offset of the directory checked against the file length. Needs no device and no
+ * context; `err_out` (may be null) receives the reason of a failure. A malformed or hostile file gives
+ * NFAI_ERR_ARG, never a crash.
+ * replaces: the header / metadata / tensor-info passes of Parser.Parse (NFAI.GGUF/Parser.cs:28-30,130-307), which
+ *           trust the counts they read. */
+int nfai_gguf_probe(const char* path, uint32_t kv_cache_size, nfai_hparams* out, char* err_out, size_t err_bytes);
+
 /* The model's geometry as it was created (filled by nfai_model_load_gguf from the file). */
 int nfai_model_get_hparams(const nfai_model* m, nfai_hparams* out);
 
@@ -231,19 +239,6 @@ int nfai_model_tune(nfai_model* m, int which, int mode, int rows_per_warp, int d
  * No counterpart in the reference. */
 int nfai_model_set_prefetch(nfai_model* m, uint64_t lookahead_bytes, uint64_t extra_bytes, int mode);
 
-/* Run the decode step as ONE persistent kernel instead of 3 + 5L kernels (grid barriers between its phases).
- * mode 0: one kernel per operation (default); mode 1: fused, the next phase's first weights are requested into
- * registers before each barrier; mode 2: fused, every warp streams its rows of ALL matrices of the step through a
- * shared-memory ring fed by bulk asynchronous copies, so the weight stream continues across the barriers.
- * Same arithmetic, same results. One GPU only; the whole grid must be co-resident. The decode graphs are
- * captured again. No counterpart in the reference (it submits and waits for every dispatch: ShaderWrapper.cs:208-245). */
-int nfai_model_set_fused_step(nfai_model* m, int mode);
-
-/* Diagnostics of the fused step: with NFAI_TRACE=1 in the environment at nfai_model_finalize, CTA 0 records a
- * %globaltimer value (nanoseconds) at every phase end and barrier of the last step; this copies up to `capacity`
- * of them out. No counterpart in the reference. */
-int nfai_model_trace(nfai_model* m, uint64_t* ns_out, int capacity, int* count);
-
 /* Number of kernel launches inside one decode step (the captured graph's kernel nodes). */
 int nfai_step_launches(const nfai_model* m, int* out);
 
@@ -293,7 +288,7 @@ size_t nfai_op_attn_scratch_bytes(uint32_t qH, uint32_t kvH, uint32_t d, uint32_
  * synchronisation): the split scratch is a 256 KiB array built into the library, so the call takes no scratch
  * pointer and performs no allocation of any kind. Inputs and outputs are still the caller's device buffers.
  *  - Geometries whose scratch (nfai_op_attn_scratch_bytes) exceeds 256 KiB are rejected with NFAI_ERR_ARG
- *    (e.g. 32 query heads of dimension 128 over more than 9 216 positions).
+ *    (e.g. 32 query heads of dimension 128 over more than 7 680 positions).
  *  - Every GPU on which the library is loaded holds those 256 KiB until the process exits.
  *  - The first call on a device resolves the array's device address (a one-time set-up); make that first call
  *    before any stream capture is begun.

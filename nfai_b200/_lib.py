@@ -55,6 +55,7 @@ SIGNATURES = {
     "nfai_model_tensor_end": (_i, [_vp]),
     "nfai_model_finalize": (_i, [_vp]),
     "nfai_model_load_gguf": (_i, [_vp, C.c_char_p, _u32, _i, _pp]),
+    "nfai_gguf_probe": (_i, [C.c_char_p, _u32, C.POINTER(HParams), C.c_char_p, _sz]),
     "nfai_model_get_hparams": (_i, [_vp, C.POINTER(HParams)]),
     "nfai_model_destroy": (_i, [_vp]),
     "nfai_prefill": (_i, [_vp, C.POINTER(_u32), _i, C.POINTER(_f), C.POINTER(_u32)]),
@@ -83,8 +84,6 @@ SIGNATURES = {
     "nfai_profile_kernel": (_i, [_vp, _i, _i, C.POINTER(_f), C.POINTER(C.c_uint64)]),
     "nfai_model_tune": (_i, [_vp, _i, _i, _i, _i, _i]),
     "nfai_model_set_prefetch": (_i, [_vp, C.c_uint64, C.c_uint64, _i]),
-    "nfai_model_set_fused_step": (_i, [_vp, _i]),
-    "nfai_model_trace": (_i, [_vp, C.POINTER(C.c_uint64), _i, C.POINTER(_i)]),
     "nfai_step_launches": (_i, [_vp, C.POINTER(_i)]),
     "nfai_op_embed": (_i, [_vp, _vp, _i, _u32, _u32, _u32, _vp]),
     "nfai_op_gemv": (_i, [_vp, _vp, _i, _u32, _u32, _vp, _vp, _f, _vp, _vp]),

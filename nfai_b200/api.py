@@ -265,17 +265,6 @@ class LlamaModel:
         check(self._lib.nfai_model_set_prefetch(self.handle, int(lookahead_bytes), int(extra_bytes), mode),
               self.ctx.handle)
 
-    def set_fused_step(self, mode):
-        """0/False = one kernel per operation, 1/True = fused with register prefetch, 2 = fused with rings."""
-        check(self._lib.nfai_model_set_fused_step(self.handle, int(mode)), self.ctx.handle)
-
-    def trace(self) -> np.ndarray:
-        buf = np.zeros(2048, np.uint64)
-        n = C.c_int()
-        check(self._lib.nfai_model_trace(self.handle, buf.ctypes.data_as(C.POINTER(C.c_uint64)), buf.size,
-                                         C.byref(n)), self.ctx.handle)
-        return buf[:n.value]
-
     def step_launches(self) -> int:
         n = C.c_int()
         check(self._lib.nfai_step_launches(self.handle, C.byref(n)), self.ctx.handle)

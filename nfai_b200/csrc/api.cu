@@ -16,7 +16,6 @@
 #include "../../include/nfai_cuda.h"
 #include "kernels.h"
 #include "gemm_tc.h"
-#include "megastep.h"
 #include "tp.h"
 
 using namespace nfai;
@@ -142,20 +141,6 @@ struct nfai_model {
   int launches_full = 0;
   uint32_t pos = 0;  // host mirror of state->pos
   GemvTune tune_qkv, tune_o, tune_gateup, tune_down, tune_head;
-  // fused decode step (one persistent kernel per token)
-  int use_fused = 0;                // 0 = one kernel per operation, 1 = fused (register prefetch), 2 = fused (rings)
-  StepDesc* desc_full = nullptr;    // device copies of the descriptors
-  StepDesc* desc_nohead = nullptr;
-  StepDesc* desc_full_ring = nullptr;
-  StepDesc* desc_nohead_ring = nullptr;
-  int ring_grid = 0, ring_stages = 0;
-  size_t ring_smem = 0;
-  LayerDesc* layer_desc = nullptr;
-  uint32_t* sync_words = nullptr;   // [0] barrier counter, [1] abort flag
-  int fused_grid = 0;
-  size_t fused_smem = 0;
-  uint32_t fused_S_max = 1;
-  unsigned long long* trace = nullptr;  // device buffer of phase time stamps (only with NFAI_TRACE=1)
   // batched prompt path (float16 weights, one GPU): chunk workspace
   bool prefill_gemm = false;
   uint32_t pf_chunk = 0;
@@ -379,19 +364,6 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
   const int wdt = hp.weight_dtype, kvdt = hp.kv_dtype;
   int n = 0;
   cudaError_t e;
-  if (m->use_fused && c->world == 1) {
-    // one persistent kernel; its grid barrier counter starts from zero at every launch
-    e = cudaMemsetAsync(m->sync_words, 0, 8, s);
-    if (e != cudaSuccess) return e;
-    if (m->use_fused == 2)
-      e = launch_fused_ring(s, wdt, kvdt, hp.d, with_head ? m->desc_full_ring : m->desc_nohead_ring, m->ring_grid, m->ring_smem,
-                            m->ring_stages);
-    else
-      e = launch_megastep(s, wdt, kvdt, hp.d, with_head ? m->desc_full : m->desc_nohead, m->fused_grid, m->fused_smem);
-    if (e != cudaSuccess) return e;
-    if (launches) *launches = 1;
-    return cudaSuccess;
-  }
   PrefetchPlanner pp = make_planner(m, with_head);
   auto end_of = [&](const Matrix& M) { return pp.off(M.ptr) + M.bytes; };
 #define STEP(call)                 \
@@ -486,10 +458,7 @@ int check_state(nfai_model* m, StepState* host_copy) {
   if (st.err) {
     uint32_t zero = 0;
     cudaMemcpy(&m->state->err, &zero, 4, cudaMemcpyHostToDevice);
-    if (st.err & 4u) {
-      cudaMemcpy(m->sync_words + 1, &zero, 4, cudaMemcpyHostToDevice);
-      return fail(c, NFAI_ERR_TIMEOUT, "a bounded device-side wait gave up");
-    }
+    if (st.err & 4u) return fail(c, NFAI_ERR_TIMEOUT, "a bounded device-side wait gave up");
     if (st.err & 1u) return fail(c, NFAI_ERR_ARG, "token id out of range (>= V)");
     return fail(c, NFAI_ERR_CONTEXT_FULL, "position reached the KV-cache capacity");
   }
@@ -902,48 +871,7 @@ int nfai_model_finalize(nfai_model* m) {
   m->nparts_alloc = (uint32_t)npart_alloc;
   const size_t o_pv = take(npart_alloc * 4);
   const size_t o_pi = take(npart_alloc * 4);
-  // fused step: shared memory, co-resident grid, attention splits (two query heads per CTA, 256 positions at least)
-  m->fused_smem = megastep_smem(hp.H, m->Fl, m->qDimL);
-  m->fused_grid = 0;
-  if (c->world == 1 && m->fused_smem <= 100 * 1024) {
-    int g = 0;
-    if (megastep_max_grid(hp.weight_dtype, hp.kv_dtype, hp.d, m->fused_smem, &g) == cudaSuccess) m->fused_grid = g;
-    cudaGetLastError();
-  }
-  {
-    const uint32_t G = m->qHl / m->kvHl;
-    const uint32_t nx = m->kvHl * ((G + kMegaHeadsPerCta - 1) / kMegaHeadsPerCta);
-    uint32_t by_len = (hp.ctx + kMegaMinChunk - 1) / kMegaMinChunk;
-    uint32_t by_grid = m->fused_grid > 0 ? (uint32_t)m->fused_grid / nx : 1;
-    if (by_grid < 1) by_grid = 1;
-    m->fused_S_max = by_len < by_grid ? by_len : by_grid;
-    if (m->fused_S_max < 1) m->fused_S_max = 1;
-    if ((uint32_t)m->fused_grid < nx) m->fused_grid = 0;  // not enough CTAs for one attention item each
-  }
-  // ring variant of the fused step: one 512-thread CTA per SM, rings as deep as shared memory allows
-  m->ring_grid = 0;
-  m->ring_stages = 0;
-  uint32_t ring_S_max = 1;
-  const uint32_t ring_heads = hp.ctx <= 4096 ? 1u : 4u;
-  const uint32_t ring_nx = ring_heads == 1 ? m->qHl : m->kvHl * ((m->qHl / m->kvHl + 3) / 4);
-  const size_t wsz = dtype_size(hp.weight_dtype);
-  if (c->world == 1 && (hp.H * wsz) % 16 == 0 && (m->qDimL * wsz) % 16 == 0 && (m->Fl * wsz) % 16 == 0) {
-    size_t rs = 0;
-    int st = 0, g = 0;
-    if (fused_ring_prepare(hp.weight_dtype, hp.kv_dtype, hp.d, hp.H, m->Fl, m->qDimL, &g, &st, &rs) == cudaSuccess && st >= 2 &&
-        (uint32_t)g >= ring_nx) {
-      m->ring_grid = g;
-      m->ring_stages = st;
-      m->ring_smem = rs;
-      uint32_t by_len = (hp.ctx + kAttnMinChunk - 1) / kAttnMinChunk;
-      uint32_t by_grid = (uint32_t)g / ring_nx;
-      ring_S_max = by_len < by_grid ? by_len : by_grid;
-      if (ring_S_max < 1) ring_S_max = 1;
-    }
-    cudaGetLastError();
-  }
-  uint32_t S_alloc = m->S_max > m->fused_S_max ? m->S_max : m->fused_S_max;
-  if (ring_S_max > S_alloc) S_alloc = ring_S_max;
+  const uint32_t S_alloc = m->S_max;
   const size_t o_ap = take(attn_part_floats(m->qHl, hp.d, S_alloc) * 4);
   const size_t o_tk = take((size_t)m->qHl * 4);  // one ticket per (kv head, head group); at most one per query head
   const size_t o_st = take(sizeof(StepState));
@@ -970,14 +898,6 @@ int nfai_model_finalize(nfai_model* m) {
   const size_t pf_part_floats = want_pf && env_int("NFAI_GEMM_SPLIT", 1) ? (size_t)148 * 128 * 128 * 2 : 0;
   const size_t o_pp = take(pf_part_floats * 4);
   const size_t o_ss = take(sample_scratch_bytes(m->Vl, nullptr));
-  const size_t o_sw = take(64);
-  const size_t o_df = take(sizeof(StepDesc));
-  const size_t o_dn = take(sizeof(StepDesc));
-  const size_t o_dfr = take(sizeof(StepDesc));
-  const size_t o_dnr = take(sizeof(StepDesc));
-  const size_t o_ld = take(sizeof(LayerDesc) * hp.L);
-  const bool want_trace = env_int("NFAI_TRACE", 0) != 0;
-  const size_t o_tr = take(want_trace ? sizeof(unsigned long long) * kTraceSlots : 8);
   cudaError_t e = cudaMalloc((void**)&m->rarena, off);
   if (e != cudaSuccess) return fail(c, NFAI_ERR_OOM, "cudaMalloc of %zu run-time bytes (KV cache etc.): %s", off, cudaGetErrorString(e));
   CU(c, cudaMemsetAsync(m->rarena, 0, off, c->stream));
@@ -1020,48 +940,6 @@ int nfai_model_finalize(nfai_model* m) {
   m->pfPart = pf_part_floats ? (float*)(m->rarena + o_pp) : nullptr;
   m->pfPartFloats = pf_part_floats;
   m->sample_scratch = m->rarena + o_ss;
-  m->sync_words = (uint32_t*)(m->rarena + o_sw);
-  m->desc_full = (StepDesc*)(m->rarena + o_df);
-  m->desc_nohead = (StepDesc*)(m->rarena + o_dn);
-  m->layer_desc = (LayerDesc*)(m->rarena + o_ld);
-  {
-    std::vector<LayerDesc> ld(hp.L);
-    for (uint32_t l = 0; l < hp.L; ++l) {
-      const LayerW& L = m->layers[l];
-      ld[l] = LayerDesc{L.qkv.ptr, L.o.ptr, L.gateup.ptr, L.down.ptr, L.attn_norm.ptr, L.ffn_norm.ptr};
-    }
-    CU(c, cudaMemcpy(m->layer_desc, ld.data(), sizeof(LayerDesc) * hp.L, cudaMemcpyHostToDevice));
-    StepDesc d{};
-    d.H = hp.H; d.L = hp.L; d.qH = m->qHl; d.kvH = m->kvHl; d.d = hp.d; d.ropeDim = hp.ropeDim; d.F = m->Fl;
-    d.V = m->Vl; d.ctx = hp.ctx; d.eps = hp.eps;
-    d.embd = m->embd.ptr; d.embd_rows = hp.V;
-    d.head = hp.tied ? (const char*)m->embd.ptr + (size_t)m->v_lo * hp.H * dtype_size(hp.weight_dtype) : m->head.ptr;
-    d.out_norm = m->out_norm.ptr; d.rope_cs = m->rope_cs; d.state = m->state; d.prompt = nullptr;
-    d.xbuf = m->xbuf; d.q = m->q; d.attn_out = m->attn_out; d.hbuf = m->hbuf; d.logits = m->logits;
-    d.part_val = m->part_val; d.part_idx = m->part_idx; d.attn_part = m->attn_part; d.tickets = m->tickets;
-    d.S_max = m->fused_S_max; d.attn_heads = kMegaHeadsPerCta; d.attn_min_chunk = kMegaMinChunk; d.kc = m->kc; d.vc = m->vc;
-    d.kv_layer_bytes = (unsigned long long)kv_layer_elems(m) * kvs;
-    d.sync_counter = m->sync_words; d.abort_flag = m->sync_words + 1;
-    d.history = m->history; d.history_cap = hp.ctx; d.with_head = 1; d.layers = m->layer_desc;
-    d.trace = want_trace ? (unsigned long long*)(m->rarena + o_tr) : nullptr;
-    m->trace = d.trace;
-    CU(c, cudaMemcpy(m->desc_full, &d, sizeof d, cudaMemcpyHostToDevice));
-    d.with_head = 0;
-    d.prompt = m->prompt;
-    CU(c, cudaMemcpy(m->desc_nohead, &d, sizeof d, cudaMemcpyHostToDevice));
-    // the ring variant has its own attention launch shape
-    m->desc_full_ring = (StepDesc*)(m->rarena + o_dfr);
-    m->desc_nohead_ring = (StepDesc*)(m->rarena + o_dnr);
-    d.S_max = ring_S_max; d.attn_heads = ring_heads; d.attn_min_chunk = kAttnMinChunk;
-    CU(c, cudaMemcpy(m->desc_nohead_ring, &d, sizeof d, cudaMemcpyHostToDevice));
-    d.with_head = 1;
-    d.prompt = nullptr;
-    CU(c, cudaMemcpy(m->desc_full_ring, &d, sizeof d, cudaMemcpyHostToDevice));
-  }
-  m->use_fused = env_int("NFAI_FUSED", 0);
-  if (m->use_fused == 2 && m->ring_grid <= 0) m->use_fused = 0;
-  if (m->use_fused == 1 && m->fused_grid <= 0) m->use_fused = 0;
-  if (m->use_fused < 0 || m->use_fused > 2) m->use_fused = 0;
   // RoPE table on the host, float32, as the reference builds its frequency table
   // (NFAI.Vulkan.Shaders/TransformerBlock.cs:33-38) and its shader forms theta = f[m] * float(pos)
   // (NFAI.Vulkan.Shaders/RoPEShader.cs:252-254); cos/sin from the host libm.
@@ -1542,51 +1420,6 @@ int nfai_model_set_prefetch(nfai_model* m, uint64_t lookahead_bytes, uint64_t ex
   m->g_full = gf;
   m->g_nohead = gn;
   m->launches_full = launches;
-  return NFAI_OK;
-}
-
-int nfai_model_set_fused_step(nfai_model* m, int enabled) {
-  int rc = ready(m);
-  if (rc) return rc;
-  nfai_ctx* c = m->ctx;
-  if (enabled < 0 || enabled > 2) return fail(c, NFAI_ERR_ARG, "mode must be 0, 1 or 2");
-  if ((enabled == 1 && m->fused_grid <= 0) || (enabled == 2 && m->ring_grid <= 0) || (enabled && c->world != 1))
-    return fail(c, NFAI_ERR_STATE, "this fused decode step is not available for this model (needs one GPU, a co-resident grid, rows that are multiples of 16 bytes and enough shared memory)");
-  const int old = m->use_fused;
-  m->use_fused = enabled;
-  if (!c->use_graph) { m->launches_full = m->use_fused ? 1 : 3 + 5 * (int)m->hp.L; return NFAI_OK; }
-  CU(c, cudaStreamSynchronize(c->stream));
-  cudaGraphExec_t gf = nullptr, gn = nullptr;
-  int launches = 0;
-  rc = capture(m, true, false, &gf, &launches);
-  if (rc == NFAI_OK) rc = capture(m, false, true, &gn, nullptr);
-  if (rc != NFAI_OK) {
-    if (gf) cudaGraphExecDestroy(gf);
-    m->use_fused = old;
-    return rc;
-  }
-  cudaGraphExecDestroy(m->g_full);
-  cudaGraphExecDestroy(m->g_nohead);
-  m->g_full = gf;
-  m->g_nohead = gn;
-  m->launches_full = launches;
-  return NFAI_OK;
-}
-
-int nfai_model_trace(nfai_model* m, uint64_t* ns_out, int capacity, int* count) {
-  int rc = ready(m);
-  if (rc) return rc;
-  nfai_ctx* c = m->ctx;
-  if (!ns_out || !count || capacity <= 0) return fail(c, NFAI_ERR_ARG, "bad argument");
-  if (!m->trace) return fail(c, NFAI_ERR_STATE, "tracing is off: set NFAI_TRACE=1 before nfai_model_finalize");
-  CU(c, cudaStreamSynchronize(c->stream));
-  std::vector<unsigned long long> buf(kTraceSlots);
-  CU(c, cudaMemcpy(buf.data(), m->trace, sizeof(unsigned long long) * kTraceSlots, cudaMemcpyDeviceToHost));
-  int n = (int)buf[0];
-  if (n > kTraceSlots - 1) n = kTraceSlots - 1;
-  if (n > capacity) n = capacity;
-  for (int i = 0; i < n; ++i) ns_out[i] = buf[1 + i];
-  *count = n;
   return NFAI_OK;
 }
 

@@ -65,7 +65,8 @@ extern "C" int nfai_op_attn_decode_static(nfai_ctx* c, const float* q, const voi
     if (!g_scratch_ptr[dev]) {
       void* p = nullptr;
       e = cudaGetSymbolAddress(&p, g_attn_scratch);
-      if (e != cudaSuccess || !p) return ctx_fail(c, NFAI_ERR_CUDA, cudaGetErrorString(e));
+      if (e != cudaSuccess) return ctx_fail(c, NFAI_ERR_CUDA, cudaGetErrorString(e));
+      if (!p) return ctx_fail(c, NFAI_ERR_CUDA, "cudaGetSymbolAddress gave a null address for the built-in scratch array");
       g_scratch_ptr[dev] = p;
     }
     scratch = g_scratch_ptr[dev];

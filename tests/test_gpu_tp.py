@@ -12,7 +12,7 @@ torch = pytest.importorskip("torch")
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank: int, world: int, port: int, key: str, push: bool, out_q):
+def _worker(rank: int, world: int, port: int, key: str, push: bool):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
 
@@ -46,10 +46,10 @@ def _worker(rank: int, world: int, port: int, key: str, push: bool, out_q):
         for _ in range(8):
             tk = O.argmax(ref.decode(tk))
             exp.append(tk)
-        out_q.put((rank, worst, list(map(int, greedy)), exp, cfg.dtype))
         dist.barrier()
         model.Dispose()
         factory.Dispose()
+        return (rank, worst, list(map(int, greedy)), exp, cfg.dtype)
     finally:
         dist.destroy_process_group()
 
@@ -59,17 +59,8 @@ def _worker(rank: int, world: int, port: int, key: str, push: bool, out_q):
 def test_tensor_parallel_matches_oracle(world, key, push):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    import torch.multiprocessing as mp
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = 29700 + (os.getpid() + world * 7 + (3 if push else 0)) % 2000
-    procs = [ctx.Process(target=_worker, args=(r, world, port, key, push, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    res = [q.get(timeout=300) for _ in procs]
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    from .mp_util import run_ranks
+    res = run_ranks(_worker, world, (key, push), timeout=300, port_base=29700 + (3 if push else 0))
     res.sort()
     for rank, worst, greedy, exp, dtype in res:
         assert worst <= (1e-4 if dtype == "f32" else 2e-3), (rank, worst)

@@ -9,7 +9,7 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank: int, world: int, port: int, out_q):
+def _worker(rank: int, world: int, port: int):
     sys.path.insert(0, ROOT)
     import torch
     import torch.distributed as dist
@@ -60,23 +60,14 @@ def _worker(rank: int, world: int, port: int, out_q):
         dist.all_reduce(part)
         x2 = x1 + part.numpy()
         err = float(np.abs(x2 - want).max() / np.abs(want).max())
-        out_q.put((rank, uid, err))
+        return (rank, uid, err)
     finally:
         dist.destroy_process_group()
 
 
 def test_two_rank_partition_and_rendezvous():
-    import torch.multiprocessing as mp
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = 29500 + os.getpid() % 2000
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    res = [q.get(timeout=120) for _ in procs]
-    for p in procs:
-        p.join(timeout=60)
-        assert p.exitcode == 0
+    from .mp_util import run_ranks
+    res = run_ranks(_worker, 2, timeout=120)
     assert {r[0] for r in res} == {0, 1}
     assert res[0][1] == res[1][1] == bytes(range(128))
     for _, _, err in res:

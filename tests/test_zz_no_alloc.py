@@ -37,18 +37,21 @@ def run_both(cuda_ctx, qH, kvH, d, seq, kvdtype, seed):
          C.c_size_t(nbytes))
     got = torch.full((qH * d,), float("nan"), dtype=torch.float32, device="cuda")
     call(cuda_ctx, "nfai_op_attn_decode_static", ptr(dq), ptr(dk), ptr(dv), code, seq, qH, kvH, d, ptr(got))
-    return host(got), host(want)
+    return host(got), host(want), (q, kc, vc)
 
 
-def test_static_scratch_matches_caller_scratch_twice_in_a_row(cuda_ctx):
+def test_static_scratch_matches_caller_scratch_twice_in_a_row(cuda_ctx, oracle):
     # first call: long enough to split the range over several CTAs (partials + tickets in the static array)
-    got, want = run_both(cuda_ctx, 32, 8, 64, 5000, np.float16, 1)
+    got, want, _ = run_both(cuda_ctx, 32, 8, 64, 5000, np.float16, 1)
     assert np.isfinite(got).all() and rel_err(got, want) < TOL
     # second call straight after: other geometry, other split count, leftovers of the first call in the array
-    got, want = run_both(cuda_ctx, 24, 8, 128, 1700, np.float32, 2)
+    got, want, (q, kc, vc) = run_both(cuda_ctx, 24, 8, 128, 1700, np.float32, 2)
     assert np.isfinite(got).all() and rel_err(got, want) < TOL
+    # the same result against the CPU restatement of the reference's three attention shaders
+    ref = oracle.attention(q, kc.astype(np.float32), vc.astype(np.float32), 1700, 24, 8, 128, 1e-5)
+    assert rel_err(got, ref) < TOL
     # and a short one that does not split at all
-    got, want = run_both(cuda_ctx, 8, 2, 32, 40, np.float32, 3)
+    got, want, _ = run_both(cuda_ctx, 8, 2, 32, 40, np.float32, 3)
     assert rel_err(got, want) < TOL
 
 
@@ -60,3 +63,15 @@ def test_static_scratch_rejects_what_it_cannot_hold(cuda_ctx):
     with pytest.raises(_lib.NfaiError) as e:
         call(cuda_ctx, "nfai_op_attn_decode_static", ptr(buf), ptr(buf), ptr(buf), _lib.F32, seq, qH, kvH, d, ptr(buf))
     assert e.value.code == _lib.ERR_ARG and "256 KiB" in str(e.value)
+
+
+def test_static_scratch_limit_is_where_the_header_says(cuda_ctx):
+    """32 query heads of dimension 128: 7 680 positions still fit the built-in array, 7 681 do not."""
+    lib = _lib.load()
+    assert lib.nfai_op_attn_scratch_bytes(32, 8, 128, 7680) <= (256 << 10) < lib.nfai_op_attn_scratch_bytes(32, 8, 128, 7681)
+    got, want, _ = run_both(cuda_ctx, 32, 8, 128, 7680, np.float16, 4)
+    assert np.isfinite(got).all() and rel_err(got, want) < TOL
+    buf = torch.zeros(16, dtype=torch.float32, device="cuda")
+    with pytest.raises(_lib.NfaiError) as e:
+        call(cuda_ctx, "nfai_op_attn_decode_static", ptr(buf), ptr(buf), ptr(buf), _lib.F16, 7681, 32, 8, 128, ptr(buf))
+    assert e.value.code == _lib.ERR_ARG
