@@ -32,30 +32,40 @@ public sealed unsafe class CudaLlamaBackend : IDisposable
 
     public void FinalizeModel() => Native.Check(Native.nfai_model_finalize(model), ctx.Handle);
 
-    // Prompt loop of RunAsync (LlamaModel.cs:103-126); returns the logits of the last prompt token.
-    public float[] Prefill(ReadOnlySpan<uint> tokens)
+    private uint lastArgMax;
+
+    // Prompt loop of RunAsync (LlamaModel.cs:103-126) as one call. Returns the logits of the last prompt token, or
+    // null when the caller does not want them read back (it then samples on the device or takes LastArgMax()).
+    public float[]? Prefill(ReadOnlySpan<uint> tokens, bool wantLogits = true)
     {
-        var logits = new float[Vocab];
+        var logits = wantLogits ? new float[Vocab] : null;
+        uint am;
         fixed (uint* pt = tokens) fixed (float* pl = logits)
-            Native.Check(Native.nfai_prefill(model, pt, tokens.Length, pl, null), ctx.Handle);
+            Native.Check(Native.nfai_prefill(model, pt, tokens.Length, pl, &am), ctx.Handle);
+        lastArgMax = am;
         return logits;
     }
 
-    // One iteration of the decode loop (LlamaModel.cs:134-173); logits go to SamplingUtils.TopP on the host.
-    public float[] Decode(uint token)
+    // One iteration of the decode loop (LlamaModel.cs:134-173). With wantLogits the 4*V bytes go to
+    // SamplingUtils.TopP on the host as in the reference; without, only the arg-max index crosses PCIe.
+    public float[]? Decode(uint token, bool wantLogits = true)
     {
-        var logits = new float[Vocab];
+        var logits = wantLogits ? new float[Vocab] : null;
+        uint am;
         fixed (float* pl = logits)
-            Native.Check(Native.nfai_decode(model, token, pl, null), ctx.Handle);
+            Native.Check(Native.nfai_decode(model, token, pl, &am), ctx.Handle);
+        lastArgMax = am;
         return logits;
     }
 
-    // Greedy variant: only the arg-max index crosses PCIe (SamplingUtils.ArgMax semantics).
+    // Index of the largest logit of the last Prefill/Decode, lowest index among equal maxima
+    // (SamplingUtils.ArgMax, SamplingUtils.cs:43-57).
+    public uint LastArgMax() => lastArgMax;
+
     public uint DecodeGreedy(uint token)
     {
-        uint am;
-        Native.Check(Native.nfai_decode(model, token, null, &am), ctx.Handle);
-        return am;
+        Decode(token, wantLogits: false);
+        return lastArgMax;
     }
 
     // SamplingUtils.TopP (SamplingUtils.cs:5-33) on the device over the logits of the last Prefill/Decode: the 513 KB

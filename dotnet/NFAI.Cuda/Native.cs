@@ -27,6 +27,7 @@ internal static unsafe partial class Native
     [DllImport(Lib)] internal static extern int nfai_tp_export_peer(IntPtr ctx, byte* outDesc, nuint outBytes);
     [DllImport(Lib)] internal static extern int nfai_tp_import_peers(IntPtr ctx, byte* descs, int n);
     [DllImport(Lib)] internal static extern int nfai_ctx_destroy(IntPtr ctx);
+    [DllImport(Lib)] internal static extern int nfai_ctx_set_wait_ns(IntPtr ctx, ulong ns);
     [DllImport(Lib)] internal static extern int nfai_model_create(IntPtr ctx, in NfaiHParams hp, out IntPtr model);
     [DllImport(Lib, CharSet = CharSet.Ansi)] internal static extern int nfai_model_tensor_begin(IntPtr model, string ggufName, int srcDType, ulong* shape, int ndim);
     [DllImport(Lib)] internal static extern int nfai_model_tensor_chunk(IntPtr model, byte* bytes, nuint nbytes);

@@ -99,6 +99,13 @@ int nfai_tp_import_peers(nfai_ctx* ctx, const void* descs, int n);
 /* replaces: LlamaModelFactory.Dispose (LlamaModelFactory.cs:24-32). */
 int nfai_ctx_destroy(nfai_ctx* ctx);
 
+/* Budget, in nanoseconds, of every device-side wait on another rank (exchange flags). Default one second, or the
+ * environment variable NFAI_WAIT_NS at context creation. A wait that runs out makes the call return
+ * NFAI_ERR_TIMEOUT; the kernel itself always returns. Takes effect for graphs captured afterwards
+ * (nfai_model_finalize, nfai_model_tune).
+ * replaces: nothing -- the reference waits on a fence without limit (VulkanBufferManager.cs:474-494). */
+int nfai_ctx_set_wait_ns(nfai_ctx* ctx, uint64_t ns);
+
 /* ---- model lifecycle: create -> tensors -> finalize -> prefill/decode -> destroy ----------------------- */
 
 /* replaces: LlamaModel ctor reading hyper-parameters (LlamaModel.cs:21-41). */
@@ -282,6 +289,30 @@ int nfai_op_attn_decode(nfai_ctx* ctx, const float* q, const void* kcache, const
                         uint32_t seq, uint32_t qH, uint32_t kvH, uint32_t d, float* out, void* scratch,
                         size_t scratch_bytes);
 size_t nfai_op_attn_scratch_bytes(uint32_t qH, uint32_t kvH, uint32_t d, uint32_t max_seq);
+
+/* ---- tensor-parallel exchange, one kernel at a time (tests and diagnostics) ---------------------------------------
+ * Under tensor parallelism the sums after the O and down projections are not a collective call: the GEMV that
+ * produces the partial rows stores them into every rank's exchange area ("push"), and the GEMV that consumes the sum
+ * waits for all ranks' flags, adds the areas' slots in rank order plus the residual while it loads x ("pull").
+ * These entry points run exactly those kernels on exchange areas the caller owns. All `world` areas may sit on ONE
+ * GPU (nfai_op_xchg_area_bytes each, zero-filled, 256-byte aligned), which is how the exchange is tested on a single
+ * GPU: rank after rank pushes, then any rank pulls. `epoch` numbers the exchange (1, 2, 3, ... per area set).
+ * A pull whose flags do not arrive within `wait_ns` nanoseconds (0 = the context's budget) returns NFAI_ERR_TIMEOUT;
+ * nothing faults or hangs and the context stays usable.
+ * No counterpart in the reference (one device; its residual adds run on the host, TransformerBlock.cs:151-161,174-181). */
+size_t nfai_op_xchg_area_bytes(void);
+/* y = W * f(x) as nfai_op_gemv. pull_epoch != 0: x is not read; x = pull_resid + sum over ranks of exchange
+ * pull_epoch, and the summed vector is also stored to pull_store. push_epoch != 0: y is not written; the rows go to
+ * rank `rank`'s slot in every area and the exchange is published. */
+int nfai_op_gemv_xchg(nfai_ctx* ctx, const void* W, int dtype, uint32_t N, uint32_t K, const float* x, const float* gain,
+                      float eps, float* y, void* const* areas, int world, int rank, uint32_t pull_epoch,
+                      const float* pull_resid, float* pull_store, uint32_t push_epoch, uint64_t wait_ns);
+/* The vocabulary-sharded LM head: push != 0 runs rank `rank`'s shard (Vl rows starting at global row v_lo) and
+ * pushes its best (value, global index) to every area; pull != 0 waits for all ranks' pairs and returns the global
+ * arg-max (lowest index among equal maxima, SamplingUtils.cs:55-56) in *argmax_out (device memory). */
+int nfai_op_lm_head_xchg(nfai_ctx* ctx, const void* W, int dtype, const float* x, const float* gain, float eps, uint32_t H,
+                         uint32_t Vl, uint32_t v_lo, float* logits, void* const* areas, int world, int rank,
+                         uint32_t epoch, int push, int pull, uint32_t* argmax_out, uint64_t wait_ns);
 
 /* Same computation as nfai_op_attn_decode, for callers that cannot allocate device memory where they run it (a
  * host working inside a fixed device-memory budget, or a per-token loop that must avoid cudaMalloc's device-wide

@@ -49,6 +49,11 @@ SIGNATURES = {
     "nfai_tp_export_peer": (_i, [_vp, _vp, _sz]),
     "nfai_tp_import_peers": (_i, [_vp, _vp, _i]),
     "nfai_ctx_destroy": (_i, [_vp]),
+    "nfai_ctx_set_wait_ns": (_i, [_vp, C.c_uint64]),
+    "nfai_op_xchg_area_bytes": (_sz, []),
+    "nfai_op_gemv_xchg": (_i, [_vp, _vp, _i, _u32, _u32, _vp, _vp, _f, _vp, _pp, _i, _i, _u32, _vp, _vp, _u32, C.c_uint64]),
+    "nfai_op_lm_head_xchg": (_i, [_vp, _vp, _i, _vp, _vp, _f, _u32, _u32, _u32, _vp, _pp, _i, _i, _u32, _i, _i, _vp,
+                                  C.c_uint64]),
     "nfai_model_create": (_i, [_vp, C.POINTER(HParams), _pp]),
     "nfai_model_tensor_begin": (_i, [_vp, C.c_char_p, _i, C.POINTER(C.c_uint64), _i]),
     "nfai_model_tensor_chunk": (_i, [_vp, _vp, _sz]),

@@ -45,6 +45,7 @@ struct nfai_ctx {
   TpComm* tp = nullptr;
   bool pdl = true;
   bool use_graph = true;
+  unsigned long long wait_ns = 1000000000ull;  // budget of every bounded device-side wait on peers (NFAI_WAIT_NS)
   std::string err;
 };
 
@@ -183,11 +184,11 @@ void read_tune(const char* name, GemvTune& t, int r_default, int u_default) {
   if (v) {
     int r = 0, u = 0, cps = 0, mode = 0, split = 0;
     int got = sscanf(v, "%d,%d,%d,%d,%d", &r, &u, &cps, &mode, &split);
-    if (got >= 2 && (r == 1 || r == 2 || r == 4) && (u == 2 || u == 3 || u == 4 || u == 6 || u == 8)) {
+    if (got >= 2 && (r == 1 || r == 2 || r == 4) && (u == 1 || u == 2 || u == 3 || u == 4 || u == 8)) {
       t.rows_per_warp = r;
       t.unroll = u;
       if (got >= 3 && cps >= 1 && cps <= 16) t.ctas_per_sm = cps;
-      if (got >= 4 && (mode == 0 || mode == 1)) t.mode = mode;
+      if (got >= 4 && (mode == 0 || mode == 1 || mode == 2)) t.mode = mode;
       if (got >= 5 && (split == 0 || split == 1 || split == 2 || split == 4 || split == 8)) t.split = split;
     }
   }
@@ -372,6 +373,32 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     if (e != cudaSuccess) return e; \
     ++n;                           \
   } while (0)
+  // Tensor parallel with peer memory: the exchanges live inside the GEMV kernels (push in the epilogue of O / down /
+  // LM head, pull in the prologue of the kernel that consumes the sum), so the step has the same launches as on one
+  // GPU. Without peer memory: NCCL all-reduce + residual-add kernel after O and down, pair gather after the LM head.
+  const bool tp_on = c->world > 1;
+  const bool fused_x = tp_on && tp_push_ready(c->tp);
+  const XchgHooks hooks = fused_x ? tp_hooks(c->tp) : XchgHooks();
+  auto pull_into = [&](GemvParams& g, uint32_t index, const float* resid, float* store) {
+    if (!fused_x) return;
+    g.tp = hooks;
+    g.tp.pull = 1;
+    g.tp.pull_index = index;
+    g.tp.pull_resid = resid;
+    g.tp.pull_store = store;
+  };
+  auto push_from = [&](GemvParams& g, uint32_t index) {
+    if (!fused_x) return;
+    const XchgHooks keep = g.tp;
+    g.tp = hooks;
+    g.tp.pull = keep.pull;
+    g.tp.pull_index = keep.pull_index;
+    g.tp.pull_resid = keep.pull_resid;
+    g.tp.pull_store = keep.pull_store;
+    g.tp.push = 1;
+    g.tp.push_index = index;
+  };
+  const bool pdl_x = pdl && (!tp_on || fused_x);  // a kernel that follows an NCCL call is launched plainly
   // the first kernel of a step must not overlap the previous step's tail: plain launch
   STEP(launch_embed(s, wdt, m->embd.ptr, hp.H, hp.V, m->state, from_prompt ? m->prompt : nullptr, 0, x_in(m, 0),
                     pp.next(0, false), false));
@@ -379,42 +406,59 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     const LayerW& LW = m->layers[l];
     GemvParams gq = qkv_params(m, l);
     gq.pf = pp.next(end_of(LW.qkv), true);
-    STEP(launch_gemv(s, wdt, kvdt, EPI_QKV_ROPE, gq, m->tune_qkv, pdl));
+    if (l > 0) pull_into(gq, 2 * l - 1, x_mid(m, l - 1), x_in(m, l));
+    STEP(launch_gemv(s, wdt, kvdt, EPI_QKV_ROPE, gq, m->tune_qkv, l > 0 ? pdl_x : pdl));
     AttnParams ga = attn_params(m, l);
     ga.pf = pp.next(end_of(LW.qkv), false);
     if (!m->attn_maps.empty()) STEP(launch_attn_ring(s, ga, m->attn_maps[l], pdl));
     else STEP(launch_attn_decode(s, kvdt, ga, pdl));
     GemvParams go = o_params(m, l);
     go.pf = pp.next(end_of(LW.o), true);
+    push_from(go, 2 * l);
     STEP(launch_gemv(s, wdt, kvdt, EPI_STORE, go, m->tune_o, pdl));
-    if (c->world > 1) {
-      e = tp_allreduce_residual(c->tp, s, m->tp_buf, x_in(m, l), x_mid(m, l), hp.H, m->state, 2 * l, &n);
+    if (tp_on && !fused_x) {
+      e = tp_allreduce_residual(c->tp, s, m->tp_buf, x_in(m, l), x_mid(m, l), hp.H, &n);
       if (e != cudaSuccess) return e;
     }
     GemvParams gg = gateup_params(m, l);
     gg.pf = pp.next(end_of(LW.gateup), true);
-    STEP(launch_gemv(s, wdt, kvdt, EPI_SILU_MUL, gg, m->tune_gateup, pdl && c->world == 1));
+    pull_into(gg, 2 * l, x_in(m, l), x_mid(m, l));
+    STEP(launch_gemv(s, wdt, kvdt, EPI_SILU_MUL, gg, m->tune_gateup, pdl_x));
     GemvParams gd = down_params(m, l);
     gd.pf = pp.next(pp.off(LW.ffn_norm.ptr) + (uint64_t)hp.H * 4, true);
+    push_from(gd, 2 * l + 1);
     STEP(launch_gemv(s, wdt, kvdt, EPI_STORE, gd, m->tune_down, pdl));
-    if (c->world > 1) {
-      e = tp_allreduce_residual(c->tp, s, m->tp_buf, x_mid(m, l), x_in(m, l + 1), hp.H, m->state, 2 * l + 1, &n);
+    if (tp_on && !fused_x) {
+      e = tp_allreduce_residual(c->tp, s, m->tp_buf, x_mid(m, l), x_in(m, l + 1), hp.H, &n);
       if (e != cudaSuccess) return e;
     }
   }
+  // exchanges of one step: 2 per layer, plus the arg-max pairs when the step ends with the LM head
+  const uint32_t per_step = 2 * hp.L + (with_head && fused_x ? 1u : 0u);
   if (with_head) {
     GemvParams gh = head_params(m);
     gh.pf = pp.next(pp.total(), true);
-    STEP(launch_gemv(s, wdt, kvdt, EPI_LOGITS, gh, m->tune_head, pdl && c->world == 1));
-    if (c->world > 1) {
+    pull_into(gh, 2 * hp.L - 1, x_mid(m, hp.L - 1), x_in(m, hp.L));
+    push_from(gh, 2 * hp.L);
+    gh.v_lo = m->v_lo;
+    STEP(launch_gemv(s, wdt, kvdt, EPI_LOGITS, gh, m->tune_head, pdl_x));
+    if (tp_on && !fused_x) {
       e = tp_gather_argmax(c->tp, s, m->part_val, m->part_idx, m->nparts, m->v_lo, &n);
       if (e != cudaSuccess) return e;
     }
-    STEP(launch_argmax_final(s, m->part_val, m->part_idx, c->world > 1 ? (uint32_t)c->world : m->nparts, m->state,
-                             nullptr, m->history, hp.ctx, pp.next(pp.total(), false), c->world > 1 ? tp_epoch_ptr(c->tp) : nullptr, 2 * hp.L,
-                             pdl && c->world == 1));
+    XchgHooks fin;
+    if (fused_x) {
+      fin = hooks;
+      fin.pull = 1;
+      fin.pull_index = 2 * hp.L;
+    }
+    STEP(launch_argmax_final(s, m->part_val, m->part_idx, tp_on ? (uint32_t)c->world : m->nparts, m->state,
+                             nullptr, m->history, hp.ctx, pp.next(pp.total(), false), tp_on ? tp_epoch_ptr(c->tp) : nullptr, per_step,
+                             fin, pdl_x));
   } else {
-    STEP(launch_advance(s, m->state, c->world > 1 ? tp_epoch_ptr(c->tp) : nullptr, 2 * hp.L, pdl && c->world == 1));
+    // head-less prompt step under tensor parallelism: the last down projection's sum is pulled by nobody (the
+    // next step starts from a fresh embedding row), which the protocol allows
+    STEP(launch_advance(s, m->state, tp_on ? tp_epoch_ptr(c->tp) : nullptr, per_step, pdl_x));
   }
 #undef STEP
   if (launches) *launches = n;
@@ -614,6 +658,10 @@ static int ctx_create_common(int device, int rank, int world, const void* uid, s
   c->world = world;
   c->pdl = env_int("NFAI_PDL", 1) != 0;
   c->use_graph = env_int("NFAI_GRAPH", 1) != 0;
+  if (const char* w = getenv("NFAI_WAIT_NS")) {
+    const unsigned long long ns = strtoull(w, nullptr, 10);
+    if (ns) c->wait_ns = ns;
+  }
   auto bail = [&](int code) {
     g_err = c->err;
     nfai_ctx_destroy(c);
@@ -642,6 +690,7 @@ static int ctx_create_common(int device, int rank, int world, const void* uid, s
   if (world > 1) {
     int rc = tp_create(&c->tp, device, rank, world, uid, uid_bytes, c->stream, c->err);
     if (rc != NFAI_OK) return bail(rc);
+    tp_set_wait_ns(c->tp, c->wait_ns);
   }
   *out = c;
   return NFAI_OK;
@@ -1081,7 +1130,7 @@ static int prefill_batched(nfai_model* m, const uint32_t* tokens, int n) {
   if (rc) return rc;
   CU(c, launch_gemv(s, hp.weight_dtype, kvdt, EPI_LOGITS, head_params(m), m->tune_head, false));
   CU(c, launch_argmax_final(s, m->part_val, m->part_idx, m->nparts, m->state, nullptr, m->history, hp.ctx, PrefetchPlan(),
-                            nullptr, 0, false));
+                            nullptr, 0, XchgHooks(), false));
   return NFAI_OK;
 }
 
@@ -1354,12 +1403,12 @@ int nfai_model_tune(nfai_model* m, int which, int mode, int rows_per_warp, int d
               : which == 3 ? &m->tune_o : which == 4 ? &m->tune_head : nullptr;
   if (!t) return fail(c, NFAI_ERR_ARG, "kernel selector must be 0..4");
   const bool even_only = which == 0 || which == 2;
-  bool ok = (mode == 0 || mode == 1) && ctas_per_sm >= 1 && ctas_per_sm <= 16 && !(even_only && rows_per_warp == 1);
+  bool ok = (mode == 0 || mode == 1 || mode == 2) && ctas_per_sm >= 1 && ctas_per_sm <= 16 && !(even_only && rows_per_warp == 1);
   if (mode == 0)
     ok = ok && (rows_per_warp == 1 || rows_per_warp == 2 || rows_per_warp == 4) && (depth == 2 || depth == 4 || depth == 8) &&
          rows_per_warp * depth <= 16;
   else
-    ok = ok && (rows_per_warp == 1 || rows_per_warp == 2) && (depth == 2 || depth == 3 || depth == 4 || depth == 6);
+    ok = ok && rows_per_warp == 2 && depth >= 1 && depth <= 4;
   if (!ok) return fail(c, NFAI_ERR_ARG, "unsupported launch shape");
   GemvTune old = *t;
   t->mode = mode;
@@ -1638,9 +1687,118 @@ int nfai_op_lm_head(nfai_ctx* c, const void* W, int dtype, const float* x, const
   p.part_val = pv;
   p.part_idx = (uint32_t*)(pv + nparts);
   cudaError_t e = launch_gemv(c->stream, dtype, NFAI_F32, EPI_LOGITS, p, t, false);
-  if (e == cudaSuccess) e = launch_argmax_final(c->stream, p.part_val, p.part_idx, nparts, nullptr, argmax_out, nullptr, 0, PrefetchPlan(), nullptr, 0, false);
+  if (e == cudaSuccess) e = launch_argmax_final(c->stream, p.part_val, p.part_idx, nparts, nullptr, argmax_out, nullptr, 0, PrefetchPlan(), nullptr, 0, XchgHooks(), false);
   cudaFreeAsync(pv, c->stream);
   return op_end(c, e);
+}
+
+// Hooks of an op-level call whose exchange areas all sit on this GPU (one per emulated rank). The epoch word
+// (c->dev_err[16]) is zero, so index = epoch - 1; tickets at c->dev_err[18..19].
+static int op_xchg_hooks(nfai_ctx* c, void* const* areas, int world, int rank, uint64_t wait_ns, XchgHooks* h) {
+  if (!areas || world < 1 || world > xchg::kMaxWorld || rank < 0 || rank >= world) return fail(c, NFAI_ERR_ARG, "bad exchange geometry");
+  char* bases[xchg::kMaxWorld] = {};
+  for (int r = 0; r < world; ++r) {
+    if (!areas[r] || ((uintptr_t)areas[r] & 255)) return fail(c, NFAI_ERR_ARG, "exchange areas must be 256-byte aligned device pointers");
+    bases[r] = (char*)areas[r];
+  }
+  h->view = xchg::make_view(bases, rank, world);
+  h->epoch_base = c->dev_err + 16;
+  h->tickets = c->dev_err + 18;
+  h->wait_ns = wait_ns ? wait_ns : c->wait_ns;
+  return NFAI_OK;
+}
+
+static int op_end_xchg(nfai_ctx* c, cudaError_t launch_err) {
+  int rc = op_end(c, launch_err);
+  if (rc) return rc;
+  uint32_t err = 0;
+  CU(c, cudaMemcpy(&err, c->dev_err, 4, cudaMemcpyDeviceToHost));
+  if (err) {
+    CU(c, cudaMemset(c->dev_err, 0, 4));
+    CU(c, cudaMemset(c->dev_err + 18, 0, 8));  // a kernel that gave up may have left its ticket word mid-count
+    if (err & 4u) return fail(c, NFAI_ERR_TIMEOUT, "a bounded device-side wait gave up");
+    return fail(c, NFAI_ERR_CUDA, "kernel reported error bits %u", err);
+  }
+  return NFAI_OK;
+}
+
+size_t nfai_op_xchg_area_bytes(void) { return xchg::kAreaBytes; }
+
+int nfai_op_gemv_xchg(nfai_ctx* c, const void* W, int dtype, uint32_t N, uint32_t K, const float* x, const float* gain, float eps,
+                      float* y, void* const* areas, int world, int rank, uint32_t pull_epoch, const float* pull_resid,
+                      float* pull_store, uint32_t push_epoch, uint64_t wait_ns) {
+  int rc = op_begin(c);
+  if (rc) return rc;
+  if (!W || bad_dtype(dtype) || !N || !K || (!pull_epoch && !x) || (!push_epoch && !y)) return fail(c, NFAI_ERR_ARG, "bad argument");
+  if (pull_epoch && (!pull_resid || !pull_store || K > xchg::kMaxH)) return fail(c, NFAI_ERR_ARG, "pull needs a residual, a store and K <= 16384");
+  if (push_epoch && N > xchg::kMaxH) return fail(c, NFAI_ERR_ARG, "push needs N <= 16384");
+  GemvParams p;
+  p.W = W; p.N = N; p.K = K; p.x = x; p.gain = gain; p.eps = eps; p.y = y;
+  p.err = c->dev_err;
+  rc = op_xchg_hooks(c, areas, world, rank, wait_ns, &p.tp);
+  if (rc) return rc;
+  if (pull_epoch) {
+    p.tp.pull = 1;
+    p.tp.pull_index = pull_epoch - 1;
+    p.tp.pull_resid = pull_resid;
+    p.tp.pull_store = pull_store;
+  }
+  if (push_epoch) {
+    p.tp.push = 1;
+    p.tp.push_index = push_epoch - 1;
+  }
+  GemvTune t;
+  read_tune("OP", t, 2, 4);
+  return op_end_xchg(c, launch_gemv(c->stream, dtype, NFAI_F32, EPI_STORE, p, t, false));
+}
+
+int nfai_op_lm_head_xchg(nfai_ctx* c, const void* W, int dtype, const float* x, const float* gain, float eps, uint32_t H,
+                         uint32_t Vl, uint32_t v_lo, float* logits, void* const* areas, int world, int rank, uint32_t epoch,
+                         int push, int pull, uint32_t* argmax_out, uint64_t wait_ns) {
+  int rc = op_begin(c);
+  if (rc) return rc;
+  if (!epoch || (push && (!W || !x || !logits || bad_dtype(dtype) || !H || !Vl)) || (pull && !argmax_out) || (!push && !pull))
+    return fail(c, NFAI_ERR_ARG, "bad argument");
+  XchgHooks h;
+  rc = op_xchg_hooks(c, areas, world, rank, wait_ns, &h);
+  if (rc) return rc;
+  cudaError_t e = cudaSuccess;
+  float* pv = nullptr;
+  if (push) {
+    GemvParams p;
+    p.W = W; p.N = Vl; p.K = H; p.x = x; p.gain = gain; p.eps = eps; p.y = logits;
+    p.err = c->dev_err;
+    p.v_lo = v_lo;
+    p.tp = h;
+    p.tp.push = 1;
+    p.tp.push_index = epoch - 1;
+    GemvTune t;
+    read_tune("OP", t, 2, 4);
+    const uint32_t nparts = gemv_grid(dtype, EPI_LOGITS, p, t);
+    CU(c, cudaMallocAsync((void**)&pv, (size_t)nparts * 8, c->stream));
+    p.part_val = pv;
+    p.part_idx = (uint32_t*)(pv + nparts);
+    e = launch_gemv(c->stream, dtype, NFAI_F32, EPI_LOGITS, p, t, false);
+  }
+  if (pull && e == cudaSuccess) {
+    h.pull = 1;
+    h.pull_index = epoch - 1;
+    // the state-less form reports a time-out through the step state only; give it one for the duration of the call
+    StepState* st = reinterpret_cast<StepState*>(c->dev_err + 32);
+    CU(c, cudaMemsetAsync(st, 0, sizeof(StepState), c->stream));
+    e = launch_argmax_final(c->stream, nullptr, nullptr, (uint32_t)world, st, argmax_out, nullptr, 0, PrefetchPlan(), nullptr, 0, h, false);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(c->dev_err, &st->err, 4, cudaMemcpyDeviceToDevice, c->stream);
+  }
+  if (pv) cudaFreeAsync(pv, c->stream);
+  return op_end_xchg(c, e);
+}
+
+int nfai_ctx_set_wait_ns(nfai_ctx* c, uint64_t ns) {
+  if (!c) return fail(nullptr, NFAI_ERR_ARG, "ctx is null");
+  if (!ns) return fail(c, NFAI_ERR_ARG, "the wait budget must be positive");
+  c->wait_ns = ns;
+  if (c->tp) tp_set_wait_ns(c->tp, ns);
+  return NFAI_OK;
 }
 
 int nfai_op_sample_top_p(nfai_ctx* c, const float* logits, uint32_t V, float temperature, float top_p, int top_k, float u,

@@ -164,6 +164,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
     }
   }
   if constexpr (EPI == EPI_LOGITS) cta_argmax_partial(p, best_v, best_i, red);
+  if constexpr (EPI == EPI_STORE) push_publish(p);
 }
 
 // Same contract for any K and any alignment (element loads); used when K is not a multiple of the vector width.
@@ -195,6 +196,7 @@ __global__ void __launch_bounds__(kThreads) gemv_scalar_kernel(const GemvParams 
     row_epilogue<KVT, R, EPI>(p, rb * R, acc, best_v, best_i);
   }
   if constexpr (EPI == EPI_LOGITS) cta_argmax_partial(p, best_v, best_i, red);
+  if constexpr (EPI == EPI_STORE) push_publish(p);
 }
 
 template <typename K>
@@ -274,12 +276,12 @@ int rows_per_warp(GemvEpilogue epi, bool vec, const GemvTune& t) {
 
 }  // namespace
 
-static bool use_ring(int wdtype, GemvEpilogue epi, const GemvParams& p, const GemvTune& t, int* R) {
-  if (t.mode != 1 || !vector_ok(wdtype, p)) return false;
-  int r = t.rows_per_warp >= 2 ? 2 : 1;
-  if (epi == EPI_QKV_ROPE || epi == EPI_SILU_MUL) r = 2;
-  if (gemv_ring_smem(p, r, t.unroll) > 227 * 1024) return false;
-  *R = r;
+static bool use_ring(int wdtype, GemvEpilogue epi, const GemvParams& p, const GemvTune& t, int* chunk) {
+  (void)epi;
+  if ((t.mode != 1 && t.mode != 2) || !vector_ok(wdtype, p)) return false;
+  const int ch = t.mode == 2 ? 4096 : 2048;
+  if (t.unroll < 1 || t.unroll > 4 || gemv_ring_smem(p, ch, t.unroll) > 227 * 1024) return false;
+  *chunk = ch;
   return true;
 }
 
@@ -307,7 +309,7 @@ static uint32_t gemv_split_log2(int wdtype, bool vec, int R, const GemvParams& p
 
 uint32_t gemv_grid(int wdtype, GemvEpilogue epi, const GemvParams& p, const GemvTune& t) {
   int ring_R = 0;
-  if (use_ring(wdtype, epi, p, t, &ring_R)) return gemv_ring_grid(p, ring_R, t.ctas_per_sm);
+  if (use_ring(wdtype, epi, p, t, &ring_R)) return gemv_ring_grid(p, t.ctas_per_sm);
   const bool vec = vector_ok(wdtype, p);
   const int R = rows_per_warp(epi, vec, t);
   const uint32_t nitems = ((p.N + R - 1) / R) << gemv_split_log2(wdtype, vec, R, p, t);

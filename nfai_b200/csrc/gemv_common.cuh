@@ -18,19 +18,54 @@ __device__ __forceinline__ void load_gain(const GemvParams& p, float* xs) {
   for (uint32_t i = threadIdx.x; i < p.K; i += kThreads) gs[i] = p.gain[i];
 }
 
+// Tensor-parallel input: x = residual + the partial vectors of all ranks, which the previous row-parallel GEMV
+// of every rank pushed into this rank's exchange area. Waits (bounded) for every rank's flag, then adds the slots
+// in rank order, the same order on every rank. CTA 0 keeps the summed vector as the residual stream.
+// When the wait gives up, error bit 4 is raised and x is zero: the kernel still runs to its end.
+__device__ __forceinline__ bool pull_wait(const GemvParams& p, uint32_t* s_flag) {
+  DeviceXchgMem mem;
+  const XchgHooks& t = p.tp;
+  const uint32_t epoch = *t.epoch_base + t.pull_index + 1;
+  if (threadIdx.x == 0) *s_flag = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < t.view.world) {
+    if (!xchg::wait_flag(mem, t.view.flags[t.view.rank] + threadIdx.x, epoch, t.wait_ns)) {
+      *s_flag = 0;
+      if (p.state) atomicOr(&p.state->err, 4u);
+      if (p.err) atomicOr(p.err, 4u);
+    }
+  }
+  __syncthreads();
+  return *s_flag != 0;
+}
+
+__device__ __forceinline__ float pull_value(const GemvParams& p, uint32_t epoch, bool ok, uint32_t i) {
+  DeviceXchgMem mem;
+  const float v = ok ? xchg::sum_slots(mem, p.tp.view, epoch, i, __ldcg(p.tp.pull_resid + i)) : 0.f;
+  if (blockIdx.x == 0 && ok) p.tp.pull_store[i] = v;
+  return v;
+}
+
 // ss = sum x^2 ; rms = sqrt(ss/K + eps) ; xs = (x / rms) * gain   (RMSNormShader.cs:136-148)
 __device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* red) {
   const uint32_t K = p.K;
   const int tid = threadIdx.x;
+  const bool pull = p.tp.pull != 0;
+  bool pull_ok = true;
+  uint32_t pull_epoch = 0;
+  if (pull) {
+    pull_ok = pull_wait(p, reinterpret_cast<uint32_t*>(red) + 31);
+    pull_epoch = *p.tp.epoch_base + p.tp.pull_index + 1;
+  }
   if (p.gain == nullptr) {
-    for (uint32_t i = tid; i < K; i += kThreads) xs[i] = p.x[i];
+    for (uint32_t i = tid; i < K; i += kThreads) xs[i] = pull ? pull_value(p, pull_epoch, pull_ok, i) : p.x[i];
     __syncthreads();
     return;
   }
   const float* gs = xs + K;  // staged by load_gain() before the dependency wait
   float ss = 0.f;
   for (uint32_t i = tid; i < K; i += kThreads) {
-    float v = p.x[i];
+    float v = pull ? pull_value(p, pull_epoch, pull_ok, i) : p.x[i];
     xs[i] = v;
     ss = fmaf(v, v, ss);
   }
@@ -45,12 +80,45 @@ __device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* re
   __syncthreads();
 }
 
+// ---- tensor-parallel push: the finished row sums of this rank go into its slot on every rank ----------------------
+template <int R>
+__device__ __forceinline__ void push_rows(const GemvParams& p, uint32_t row0, const float (&acc)[R]) {
+  DeviceXchgMem mem;
+  const uint32_t epoch = *p.tp.epoch_base + p.tp.push_index + 1;
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+    if (row0 + r < p.N) xchg::push_value(mem, p.tp.view, epoch, row0 + r, acc[r]);
+}
+
+// Every thread of every CTA of a pushing kernel calls this once, after its last row: the CTAs draw tickets and
+// the last one tells every rank that this rank's vector is complete. The barrier orders the CTA's peer stores
+// before thread 0's system-scope fence; the ticket (device scope) makes the last CTA's fence cover all of them.
+__device__ __forceinline__ void push_publish(const GemvParams& p) {
+  if (!p.tp.push) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    DeviceXchgMem mem;
+    uint32_t* ticket = p.tp.tickets + (p.tp.push_index & 1u);
+    __threadfence_system();
+    const uint32_t t = atomicAdd(ticket, 1u);
+    if (t == gridDim.x - 1) {
+      *ticket = 0;  // the next pushing kernel that uses this word starts after this one has ended
+      __threadfence_system();
+      xchg::publish(mem, p.tp.view, *p.tp.epoch_base + p.tp.push_index + 1);
+    }
+  }
+}
+
 // ---- epilogues (lane 0 of the warp holds the R finished row sums of one row block) --------------------------------
 template <typename KVT, int R, int EPI>
 __device__ __forceinline__ void row_epilogue(const GemvParams& p, uint32_t row0, const float (&acc)[R], float& best_v,
                                              uint32_t& best_i) {
   if ((threadIdx.x & 31) != 0) return;
   if constexpr (EPI == EPI_STORE) {
+    if (p.tp.push) {
+      push_rows<R>(p, row0, acc);
+      return;
+    }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       uint32_t n = row0 + r;
@@ -156,6 +224,10 @@ __device__ __forceinline__ void row_epilogue_pre(const GemvParams& p, uint32_t r
                                                  const float (&pre)[R], uint32_t pos, float& best_v, uint32_t& best_i) {
   if ((threadIdx.x & 31) != 0) return;
   if constexpr (EPI == EPI_STORE) {
+    if (p.tp.push) {
+      push_rows<R>(p, row0, acc);
+      return;
+    }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       uint32_t n = row0 + r;
@@ -201,10 +273,15 @@ __device__ __forceinline__ void row_epilogue_pre(const GemvParams& p, uint32_t r
   }
 }
 
-// EPI_LOGITS: one (max, lowest index) partial per CTA.
+// EPI_LOGITS: one (max, lowest index) partial per CTA. Under tensor parallelism the CTA that finishes last also
+// reduces all partials of this rank and pushes (value, global index) to every rank: the arg-max exchange needs no
+// kernel of its own.
 __device__ __forceinline__ void cta_argmax_partial(const GemvParams& p, float best_v, uint32_t best_i, float* red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   uint32_t* redi = reinterpret_cast<uint32_t*>(red);
+  auto better = [](float v, uint32_t i, float bv, uint32_t bi) {
+    return i != 0xffffffffu && (bi == 0xffffffffu || v > bv || (v == bv && i < bi));
+  };
   __syncthreads();  // red[] may still be read by the prologue of a slower warp
   if (lane == 0) {
     red[warp] = best_v;
@@ -214,16 +291,58 @@ __device__ __forceinline__ void cta_argmax_partial(const GemvParams& p, float be
   if (threadIdx.x == 0) {
     float v = red[0];
     uint32_t ix = redi[kWarps];
-    for (int w = 1; w < kWarps; ++w) {
-      float wv = red[w];
-      uint32_t wi = redi[kWarps + w];
-      if (wi != 0xffffffffu && (ix == 0xffffffffu || wv > v || (wv == v && wi < ix))) {
-        v = wv;
-        ix = wi;
+    for (int w = 1; w < kWarps; ++w)
+      if (better(red[w], redi[kWarps + w], v, ix)) {
+        v = red[w];
+        ix = redi[kWarps + w];
       }
-    }
     p.part_val[blockIdx.x] = v;
     p.part_idx[blockIdx.x] = ix;
+  }
+  if (!p.tp.push) return;
+  uint32_t* s_last = redi + 30;
+  uint32_t* ticket = p.tp.tickets + (p.tp.push_index & 1u);
+  if (threadIdx.x == 0) {
+    __threadfence();
+    *s_last = atomicAdd(ticket, 1u) == gridDim.x - 1 ? 1u : 0u;
+  }
+  __syncthreads();
+  if (!*s_last) return;
+  __threadfence();
+  float bv = 0.f;
+  uint32_t bi = 0xffffffffu;
+  for (uint32_t i = threadIdx.x; i < gridDim.x; i += kThreads) {
+    const float v = __ldcg(p.part_val + i);
+    const uint32_t ix = __ldcg(p.part_idx + i);
+    if (better(v, ix, bv, bi)) {
+      bv = v;
+      bi = ix;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, bv, bi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  __syncthreads();
+  if (lane == 0) {
+    red[warp] = bv;
+    redi[kWarps + warp] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 0; w < kWarps; ++w)
+      if (w == 0 || better(red[w], redi[kWarps + w], bv, bi)) {
+        bv = red[w];
+        bi = redi[kWarps + w];
+      }
+    *ticket = 0;
+    DeviceXchgMem mem;
+    xchg::push_pair(mem, p.tp.view, *p.tp.epoch_base + p.tp.push_index + 1, bv, bi == 0xffffffffu ? bi : bi + p.v_lo);
   }
 }
 

@@ -5,7 +5,26 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include "xchg_protocol.h"
+
 namespace nfai {
+
+// Tensor-parallel hooks of a GEMV launch (world <= 1: none of it is touched). The partial sums of a row-parallel
+// matrix (O and down projections) never go through a separate collective kernel: the GEMV that produces them
+// stores them straight into every rank's exchange area (push) and the GEMV that consumes the sum waits for all
+// ranks' flags and adds the slots in rank order while it loads x (pull). Protocol: xchg_protocol.h.
+struct XchgHooks {
+  xchg::View view{};                     // every rank's exchange area (own entry = local memory)
+  const uint32_t* epoch_base = nullptr;  // device word: exchanges completed on this context before this step
+  uint32_t* tickets = nullptr;           // two local words: CTAs of a pushing kernel draw tickets, the last publishes
+  unsigned long long wait_ns = 1000000000ull;  // budget of the flag wait; afterwards error bit 4 and a zero x
+  int pull = 0;                          // x = pull_resid + sum over ranks of exchange pull_index of this step
+  uint32_t pull_index = 0;
+  const float* pull_resid = nullptr;
+  float* pull_store = nullptr;           // CTA 0 also stores the summed x here (the residual stream)
+  int push = 0;                          // row sums go to every rank's slot (exchange push_index) instead of y
+  uint32_t push_index = 0;
+};
 
 // Kernels that stage their stream in shared memory ask for the largest shared-memory carve-out. Kernels that
 // stream through registers must NOT: loads in flight occupy L1 lines, so shrinking the L1 cuts their bandwidth
@@ -89,21 +108,26 @@ struct GemvParams {
   PrefetchPlan pf;
   uint32_t* err = nullptr;  // optional device word for error bits when there is no StepState (4 = a bounded wait gave up)
   uint32_t split_log2 = 0;  // filled in by launch_gemv: log2 of the warps that share one row block
+  XchgHooks tp;             // tensor-parallel push / pull (see XchgHooks)
+  // EPI_LOGITS under tensor parallelism: the last CTA reduces the per-CTA partials to this rank's best
+  // (value, global index = v_lo + row) and pushes the pair to every rank (exchange tp.push_index)
+  uint32_t v_lo = 0;
 };
 
 // Tunable launch shape of the GEMV family.
 struct GemvTune {
-  int mode = 0;           // 0 = register double-buffered streamer, 1 = shared-memory ring fed by bulk copies
-  int rows_per_warp = 2;  // mode 0: 1, 2 or 4; mode 1: 1 or 2 (EPI_QKV_ROPE and EPI_SILU_MUL need an even value)
-  int unroll = 4;         // mode 0: 16-byte loads in flight per row per lane (2, 4 or 8); mode 1: ring stages (2, 3, 4, 6)
+  int mode = 0;           // 0 = register double-buffered streamer, 1 / 2 = shared-memory rings fed by bulk copies,
+                          // stages of 2 rows x 2 KB / 2 rows x 4 KB
+  int rows_per_warp = 2;  // mode 0: 1, 2 or 4 (EPI_QKV_ROPE and EPI_SILU_MUL need an even value); ring modes: always 2
+  int unroll = 4;         // mode 0: 16-byte loads in flight per row per lane (2, 4 or 8); ring modes: stages per warp (1-4)
   int ctas_per_sm = 2;    // persistent grid = min(needed, 148 * ctas_per_sm) CTAs of 256 threads
   int split = 0;          // mode 0: warps sharing one row block (1, 2, 4, 8); 0 = chosen from the matrix shape
 };
 
-size_t gemv_ring_smem(const GemvParams& p, int R, int S);
-uint32_t gemv_ring_grid(const GemvParams& p, int R, int ctas_per_sm);
-cudaError_t launch_gemv_ring(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue epi, const GemvParams& p, int R,
-                             int S, int ctas_per_sm, bool pdl);
+size_t gemv_ring_smem(const GemvParams& p, int chunk_bytes, int S);
+uint32_t gemv_ring_grid(const GemvParams& p, int ctas_per_sm);
+cudaError_t launch_gemv_ring(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue epi, const GemvParams& p,
+                             int chunk_bytes, int S, int ctas_per_sm, bool pdl);
 
 // Number of CTAs the launch will use (the LM head needs it to size its partial buffers).
 uint32_t gemv_grid(int wdtype, GemvEpilogue epi, const GemvParams& p, const GemvTune& t);
@@ -164,7 +188,8 @@ cudaError_t launch_embed(cudaStream_t s, int wdtype, const void* E, uint32_t H, 
 // token and advance the position.
 cudaError_t launch_argmax_final(cudaStream_t s, const float* part_val, const uint32_t* part_idx, uint32_t nparts,
                                 StepState* state, uint32_t* argmax_out, uint32_t* history, uint32_t history_cap,
-                                const PrefetchPlan& pf, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl);
+                                const PrefetchPlan& pf, uint32_t* xchg_epoch, uint32_t xchg_per_step, const XchgHooks& tp,
+                                bool pdl);
 // Head-less prompt step: position and prompt cursor advance by one.
 // xchg_epoch (may be null) counts the tensor-parallel exchanges completed on this context; a step adds its own.
 cudaError_t launch_advance(cudaStream_t s, StepState* state, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl);

@@ -46,20 +46,37 @@ __global__ void __launch_bounds__(256) argmax_final_kernel(const float* __restri
                                                           const uint32_t* __restrict__ part_idx, uint32_t nparts,
                                                           StepState* state, uint32_t* argmax_out, uint32_t* history,
                                                           uint32_t history_cap, const PrefetchPlan pf,
-                                                          uint32_t* xchg_epoch, uint32_t xchg_per_step) {
+                                                          uint32_t* xchg_epoch, uint32_t xchg_per_step,
+                                                          const XchgHooks tp) {
   __shared__ float sv[256];
   __shared__ uint32_t si[256];
+  __shared__ uint32_t s_ok;
   prefetch_plan(pf, kPrefetchChunk);
   pdl_launch_dependents();
   pdl_wait();
   float bv = -INFINITY;
   uint32_t bi = 0xffffffffu;
-  for (uint32_t i = threadIdx.x; i < nparts; i += blockDim.x) {
-    float v = part_val[i];
-    uint32_t ix = part_idx[i];
-    if (ix != 0xffffffffu && (bi == 0xffffffffu || v > bv || (v == bv && ix < bi))) {
-      bv = v;
-      bi = ix;
+  if (tp.pull) {
+    // tensor parallel: every rank's LM-head kernel pushed its best (value, global index) into this rank's area
+    DeviceXchgMem mem;
+    const uint32_t epoch = *tp.epoch_base + tp.pull_index + 1;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if ((int)threadIdx.x < tp.view.world &&
+        !xchg::wait_flag(mem, tp.view.pair_flags[tp.view.rank] + threadIdx.x, epoch, tp.wait_ns)) {
+      s_ok = 0;
+      if (state) atomicOr(&state->err, 4u);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && s_ok) xchg::best_pair(mem, tp.view, epoch, &bv, &bi);
+  } else {
+    for (uint32_t i = threadIdx.x; i < nparts; i += blockDim.x) {
+      float v = part_val[i];
+      uint32_t ix = part_idx[i];
+      if (ix != 0xffffffffu && (bi == 0xffffffffu || v > bv || (v == bv && ix < bi))) {
+        bv = v;
+        bi = ix;
+      }
     }
   }
   sv[threadIdx.x] = bv;
@@ -131,11 +148,12 @@ cudaError_t launch_embed(cudaStream_t s, int wdtype, const void* E, uint32_t H, 
 
 cudaError_t launch_argmax_final(cudaStream_t s, const float* part_val, const uint32_t* part_idx, uint32_t nparts,
                                 StepState* state, uint32_t* argmax_out, uint32_t* history, uint32_t history_cap,
-                                const PrefetchPlan& pf, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl) {
+                                const PrefetchPlan& pf, uint32_t* xchg_epoch, uint32_t xchg_per_step, const XchgHooks& tp,
+                                bool pdl) {
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t cfg = make_cfg(dim3(1), dim3(256), s, attr, pdl);
   return cudaLaunchKernelEx(&cfg, argmax_final_kernel, part_val, part_idx, nparts, state, argmax_out, history,
-                            history_cap, pf, xchg_epoch, xchg_per_step);
+                            history_cap, pf, xchg_epoch, xchg_per_step, tp);
 }
 
 cudaError_t launch_advance(cudaStream_t s, StepState* state, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl) {

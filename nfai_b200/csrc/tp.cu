@@ -106,19 +106,8 @@ __global__ void unpack_pairs_kernel(const uint2* __restrict__ pairs, int world, 
 
 }  // namespace
 
-// Peer-memory exchange area of one rank, written by every rank (this one included) over NVLink:
-//   slots[parity][src][kPushMaxH] float32 partial sums, flags[src] = epoch of the last exchange src has delivered.
-constexpr uint32_t kPushMaxH = 16384;
-constexpr int kPushMaxWorld = 8;
-constexpr size_t kPushSlotFloats = (size_t)2 * kPushMaxWorld * kPushMaxH;
-constexpr size_t kPushBytes = kPushSlotFloats * 4 + 512;  // slots, 256 bytes of flags, 256 bytes local (epoch word)
-
-struct PushView {
-  float* slots[kPushMaxWorld];     // slot area of every rank (own entry = local pointer)
-  uint32_t* flags[kPushMaxWorld];  // flag words of every rank
-  int rank, world;
-};
-
+// Peer-memory exchange area of one rank, written by every rank (this one included) over NVLink; layout and
+// protocol in xchg_protocol.h.
 struct PeerDesc {  // 128 bytes on the wire
   int32_t pid;
   int32_t device;
@@ -135,73 +124,11 @@ struct TpComm {
   float* full_logits = nullptr; // [world * Vl], allocated on first use
   size_t full_logits_elems = 0;
   char* push_local = nullptr;   // this rank's exchange area (its own cudaMalloc: it is exported whole)
-  void* push_opened[kPushMaxWorld] = {};  // IPC mappings to close
-  PushView view{};
+  void* push_opened[xchg::kMaxWorld] = {};  // IPC mappings to close
+  xchg::View view{};
   bool push_ready = false;
+  unsigned long long wait_ns = 1000000000ull;
 };
-
-namespace {
-
-constexpr unsigned long long kPushWaitNs = 1000000000ull;
-
-__device__ __forceinline__ unsigned long long tp_global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
-// One-shot push all-reduce + residual add, one CTA. Every rank stores its partial vector into its slot on every
-// rank, publishes the exchange's epoch with a system-scope release, waits (bounded) until every rank's epoch has
-// arrived in its own flags, then sums the slots in rank order -- the same order on every rank, so all ranks hold
-// bit-identical residual streams.
-__global__ void __launch_bounds__(1024) push_allreduce_residual_kernel(PushView pv, const float* __restrict__ partial,
-                                                                      const float* __restrict__ resid,
-                                                                      float* __restrict__ x_out, uint32_t H,
-                                                                      StepState* state, const uint32_t* epoch_base,
-                                                                      uint32_t index_in_step) {
-  __shared__ uint32_t s_ok;
-  const uint32_t epoch = *epoch_base + index_in_step + 1;
-  const uint32_t parity = epoch & 1u;
-  const int tid = threadIdx.x;
-  if (tid == 0) s_ok = 1;
-  for (uint32_t i = tid; i < H; i += blockDim.x) {
-    const float v = partial[i];
-    for (int dst = 0; dst < pv.world; ++dst)
-      pv.slots[dst][((size_t)parity * kPushMaxWorld + pv.rank) * kPushMaxH + i] = v;
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (tid < pv.world) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pv.flags[tid] + pv.rank), "r"(epoch) : "memory");
-    // wait for rank `tid`'s epoch in this rank's own flags
-    const uint32_t* f = pv.flags[pv.rank] + tid;
-    uint32_t seen;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
-    if ((int32_t)(seen - epoch) < 0) {
-      const unsigned long long t0 = tp_global_ns();
-      uint32_t polls = 0;
-      while (true) {
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
-        if ((int32_t)(seen - epoch) >= 0) break;
-        if ((++polls & 63u) == 0 && tp_global_ns() - t0 > kPushWaitNs) {
-          s_ok = 0;
-          atomicOr(&state->err, 4u);
-          break;
-        }
-      }
-    }
-  }
-  __syncthreads();
-  if (!s_ok) return;
-  const float* mine = pv.slots[pv.rank] + (size_t)parity * kPushMaxWorld * kPushMaxH;
-  for (uint32_t i = tid; i < H; i += blockDim.x) {
-    float sum = 0.f;
-    for (int src = 0; src < pv.world; ++src) sum += __ldcg(mine + (size_t)src * kPushMaxH + i);
-    x_out[i] = resid[i] + sum;
-  }
-}
-
-}  // namespace
 
 int tp_unique_id(void* out, size_t out_bytes, std::string& err) {
   if (!out || out_bytes < sizeof(ncclUniqueId)) {
@@ -239,8 +166,8 @@ int tp_create(TpComm** out, int device, int rank, int world, const void* uid, si
     delete tp;
     return NFAI_ERR_NCCL;
   }
-  cudaError_t e = cudaMalloc((void**)&tp->push_local, kPushBytes);  // own allocation: it is exported whole
-  if (e == cudaSuccess) e = cudaMemset(tp->push_local, 0, kPushBytes);
+  cudaError_t e = cudaMalloc((void**)&tp->push_local, xchg::kAreaBytes);  // own allocation: it is exported whole
+  if (e == cudaSuccess) e = cudaMemset(tp->push_local, 0, xchg::kAreaBytes);
   if (e == cudaSuccess) e = cudaMalloc((void**)&tp->pairs, sizeof(uint2) * 8);
   if (e != cudaSuccess) {
     err = std::string("cudaMalloc: ") + cudaGetErrorString(e);
@@ -254,7 +181,7 @@ int tp_create(TpComm** out, int device, int rank, int world, const void* uid, si
 
 void tp_destroy(TpComm* tp) {
   if (!tp) return;
-  for (int i = 0; i < kPushMaxWorld; ++i)
+  for (int i = 0; i < xchg::kMaxWorld; ++i)
     if (tp->push_opened[i]) cudaIpcCloseMemHandle(tp->push_opened[i]);
   if (tp->push_local) cudaFree(tp->push_local);
   if (tp->comm) g_nccl.CommDestroy(tp->comm);
@@ -263,20 +190,30 @@ void tp_destroy(TpComm* tp) {
   delete tp;
 }
 
+// Baseline exchange (kept for comparison and for peers without mutual memory access): NCCL all-reduce of the
+// partial vector, then one kernel that adds the residual.
 cudaError_t tp_allreduce_residual(TpComm* tp, cudaStream_t s, float* buf, const float* resid, float* x_out, uint32_t H,
-                                  StepState* state, uint32_t index_in_step, int* launches) {
-  if (tp->push_ready && H <= kPushMaxH) {
-    push_allreduce_residual_kernel<<<1, 1024, 0, s>>>(tp->view, buf, resid, x_out, H, state, tp_epoch_ptr(tp),
-                                                       index_in_step);
-    if (launches) *launches += 1;
-    return cudaGetLastError();
-  }
+                                  int* launches) {
   ncclResult_t r = g_nccl.AllReduce(buf, buf, H, ncclFloat, ncclSum, tp->comm, s);
   if (r != ncclSuccess) return cudaErrorUnknown;
   add_residual_kernel<<<(H + 255) / 256, 256, 0, s>>>(buf, resid, x_out, H);
   if (launches) *launches += 1;
   return cudaGetLastError();
 }
+
+bool tp_push_ready(const TpComm* tp) { return tp->push_ready; }
+
+// Hooks for the kernels of one step; the caller fills in pull / push and the exchange indices.
+XchgHooks tp_hooks(TpComm* tp) {
+  XchgHooks h;
+  h.view = tp->view;
+  h.epoch_base = tp_epoch_ptr(tp);
+  h.tickets = tp_epoch_ptr(tp) + 2;
+  h.wait_ns = tp->wait_ns;
+  return h;
+}
+
+void tp_set_wait_ns(TpComm* tp, unsigned long long ns) { tp->wait_ns = ns ? ns : 1; }
 
 cudaError_t tp_gather_argmax(TpComm* tp, cudaStream_t s, float* part_val, uint32_t* part_idx, uint32_t nparts,
                              uint32_t v_lo, int* launches) {
@@ -290,7 +227,7 @@ cudaError_t tp_gather_argmax(TpComm* tp, cudaStream_t s, float* part_val, uint32
   return cudaGetLastError();
 }
 
-uint32_t* tp_epoch_ptr(TpComm* tp) { return reinterpret_cast<uint32_t*>(tp->push_local + kPushSlotFloats * 4 + 256); }
+uint32_t* tp_epoch_ptr(TpComm* tp) { return reinterpret_cast<uint32_t*>(tp->push_local + xchg::kLocalOffset); }
 
 int tp_export_peer_desc(TpComm* tp, void* out, size_t out_bytes, std::string& err) {
   if (!out || out_bytes < kTpPeerDescBytes) {
@@ -317,9 +254,7 @@ int tp_import_peer_descs(TpComm* tp, const void* descs, int n, std::string& err)
     return NFAI_ERR_ARG;
   }
   const PeerDesc* d = reinterpret_cast<const PeerDesc*>(descs);
-  PushView v{};
-  v.rank = tp->rank;
-  v.world = tp->world;
+  char* bases[xchg::kMaxWorld] = {};
   for (int r = 0; r < n; ++r) {
     char* base = nullptr;
     if (r == tp->rank) {
@@ -349,10 +284,9 @@ int tp_import_peer_descs(TpComm* tp, const void* descs, int n, std::string& err)
       tp->push_opened[r] = p;
       base = (char*)p;
     }
-    v.slots[r] = reinterpret_cast<float*>(base);
-    v.flags[r] = reinterpret_cast<uint32_t*>(base + kPushSlotFloats * 4);
+    bases[r] = base;
   }
-  tp->view = v;
+  tp->view = xchg::make_view(bases, tp->rank, tp->world);
   tp->push_ready = true;
   return NFAI_OK;
 }

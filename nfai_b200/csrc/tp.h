@@ -23,10 +23,15 @@ void tp_destroy(TpComm* tp);
 // Device word counting the exchanges completed on this context (advanced by the last kernel of every step).
 uint32_t* tp_epoch_ptr(TpComm* tp);
 
-// `index_in_step` numbers the exchanges of one step (0 .. 2L-1); together with the context's epoch word it gives every
-// exchange of the run its own epoch, which is what the peer-memory path uses as its flag value.
+// Baseline: NCCL all-reduce of buf[0..H) plus a residual-add kernel: x_out = resid + sum over ranks.
 cudaError_t tp_allreduce_residual(TpComm* tp, cudaStream_t s, float* buf, const float* resid, float* x_out, uint32_t H,
-                                  StepState* state, uint32_t index_in_step, int* launches);
+                                  int* launches);
+
+// After tp_import_peer_descs: the exchanges run inside the GEMV kernels (push in the epilogue of the producer, pull
+// in the prologue of the consumer; xchg_protocol.h). tp_hooks gives the view, epoch word, tickets and wait budget.
+bool tp_push_ready(const TpComm* tp);
+XchgHooks tp_hooks(TpComm* tp);
+void tp_set_wait_ns(TpComm* tp, unsigned long long ns);
 
 // Peer-memory exchange buffers. Every rank exports a 128-byte descriptor of its buffer (process id, device
 // pointer, CUDA IPC handle); the host gathers the descriptors of all ranks and hands them to every rank. After the

@@ -34,3 +34,29 @@ def test_context_from_c(tmp_path):
     exe = _compile(tmp_path)
     r = subprocess.run([exe, "gpu"], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, (r.returncode, r.stdout, r.stderr)
+
+
+def _compile_xchg_model(tmp_path):
+    gxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else shutil.which("g++")
+    if not gxx:
+        pytest.skip("no C++ compiler")
+    exe = str(tmp_path / "xchg_model")
+    subprocess.run([gxx, "-O2", "-std=c++17", "-pthread", "-Wall", "-Werror", "-I", os.path.join(ROOT, "nfai_b200", "csrc"),
+                    os.path.join(ROOT, "tests", "cabi", "xchg_model.cpp"), "-o", exe], check=True)
+    return exe
+
+
+@pytest.mark.parametrize("world,rounds,H", [(2, 400, 32), (4, 300, 64), (8, 150, 128)])
+def test_exchange_protocol_with_cpu_threads_as_ranks(tmp_path, world, rounds, H):
+    """The epoch / parity protocol of the tensor-parallel exchange (the header the kernels compile) run by CPU threads:
+    bit-identical sums on every rank, lowest-index arg-max, epochs across the 32-bit wrap."""
+    exe = _compile_xchg_model(tmp_path)
+    r = subprocess.run([exe, str(world), str(rounds), str(H)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, (r.stdout, r.stderr)
+
+
+def test_exchange_protocol_gives_up_when_a_rank_is_gone(tmp_path):
+    """A rank that stops publishing: the others leave their bounded wait with a time-out, nothing hangs."""
+    exe = _compile_xchg_model(tmp_path)
+    r = subprocess.run([exe, "4", "100", "64", "2", "37"], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0, (r.stdout, r.stderr)
