@@ -32,10 +32,13 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture
-# summarised in profiles/gemv_decode_llama1b_f16_ncu.md (configs[1], one GPU)
-NCU_TRAFFIC_BYTES = {("c1", 1): 67155200 + 453376}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel (FFN gate/up GEMV of configs[1]
+# on one GPU), from an ncu capture of this kernel; it goes stale when the kernel's memory behaviour changes, so the
+# capture it came from is named beside it.
+NCU_TRAFFIC = {("c1", 1): {"bytes": 67155200 + 453376,
+                           "capture": "ncu --set full, one launch of the gate/up GEMV inside a decode step"}}
 PROMPT_LEN = 128
+MIN_TIMED_S = 1.0  # the K-step loop is repeated until this much device time has been measured; the median is reported
 
 
 def measured_peak():
@@ -45,6 +48,37 @@ def measured_peak():
             return float(json.load(fh)["hbm_gbs"]), "measured"
     except Exception:
         return FALLBACK_HBM_GBS, "fallback"
+
+
+def measured_tflops():
+    """(sustained, burst) dense bf16 TFLOP/s of this pool's B200s; the fallback is an earlier measurement."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as fh:
+            d = json.load(fh)
+            return float(d["bf16_tflops_sustained"]), float(d["bf16_tflops"]), "measured"
+    except Exception:
+        return 1400.0, 1590.0, "fallback"
+
+
+def parity_against_fixture(logits, greedy_tokens):
+    """The benchmark model against the committed fixture of the same model: logits after the prompt at 2 048 fixed
+    indices (CPU oracle and one-GPU run) and the first greedy tokens."""
+    import numpy as np
+    path = os.path.join(ROOT, "tests", "golden", "bench_c1_parity.npz")
+    if not os.path.exists(path):
+        return {"unavailable": "fixture missing"}
+    g = np.load(path)
+    sub = np.asarray(logits, np.float32)[g["idx"]]
+    out = {"max_abs_vs_oracle": float(np.abs(sub - g["oracle_logits"]).max()), "tolerance_abs": 2e-2,
+           "argmax_equals_oracle": bool(int(np.argmax(logits)) == int(g["oracle_argmax"]))}
+    n = min(len(greedy_tokens), len(g["oracle_greedy"]) - 1)
+    out["greedy_tokens_equal_oracle"] = int(sum(int(a) == int(b) for a, b in zip(greedy_tokens[:n], g["oracle_greedy"][1:1 + n])))
+    out["greedy_tokens_compared"] = n
+    if "gpu1_logits" in g.files:
+        out["max_abs_vs_tp1_golden"] = float(np.abs(sub - g["gpu1_logits"]).max())
+        out["tokens_equal"] = bool(all(int(a) == int(b) for a, b in zip(greedy_tokens[:n], g["gpu1_greedy"][1:1 + n])))
+    return out
 
 
 class ClockSampler:
@@ -206,38 +240,64 @@ def run_ours(args, cfg):
     barrier()
     prefill_s = time.perf_counter() - t_pf
 
-    # ---- value: device-resident greedy decode, CUDA events on the library's stream
+    # ---- parity of the model being timed (every GPU count): logits after the prompt (all-gathered under tensor
+    # parallelism) and the first greedy tokens against the committed fixture of the same seeded model
+    parity = None
+    if args.config == "c1" and PROMPT_LEN == 128 and args.seed == 0:
+        model.reset()
+        lg, am_p = model.prefill(prompt, want_logits=True)
+        g_toks, _ = model.decode_greedy(am_p, 15)
+        if rank == 0:
+            parity = parity_against_fixture(lg, [int(t) for t in g_toks])
+        model.set_position(PROMPT_LEN)
+
+    # ---- value: device-resident greedy decode, CUDA events on the library's stream. The K-step loop is repeated
+    # from the same position until at least MIN_TIMED_S of device time has been measured; the median counts.
+    import statistics as st
     toks_w, _ = model.decode_greedy(am, W)
+    first_tok = int(toks_w[-1])
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    barrier()
-    toks, ms = model.decode_greedy(int(toks_w[-1]), K)
-    barrier()
-    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    reps_ms, toks = [], None
+    while True:
+        model.set_position(PROMPT_LEN + W)
+        barrier()
+        toks_r, ms_r = model.decode_greedy(first_tok, K)
+        barrier()
+        t = torch.tensor([ms_r], dtype=torch.float64, device="cuda")
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        reps_ms.append(float(t.item()))
+        toks = toks_r if toks is None else toks
+        if sum(reps_ms) >= MIN_TIMED_S * 1e3 or len(reps_ms) >= 400:
+            break
+    ms = st.median(reps_ms)
 
-    # ---- e2e: the reference-facing call per token, host token in / arg-max out
-    model.set_position(PROMPT_LEN)
-    tk = am
-    for _ in range(W):
-        _, tk = model.decode(tk, want_logits=False)
-    barrier()
-    t0 = time.perf_counter()
-    e2e_toks = []
-    for _ in range(K):
-        _, tk = model.decode(tk, want_logits=False)
-        e2e_toks.append(tk)
-    barrier()
-    e2e_s = time.perf_counter() - t0
-    t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_s = float(t.item())
+    # ---- e2e: the reference-facing call per token, host token in / arg-max out, repeated the same way
+    e2e_reps, e2e_toks = [], None
+    while True:
+        model.set_position(PROMPT_LEN)
+        tk = am
+        for _ in range(W):
+            _, tk = model.decode(tk, want_logits=False)
+        barrier()
+        t0 = time.perf_counter()
+        seq = []
+        for _ in range(K):
+            _, tk = model.decode(tk, want_logits=False)
+            seq.append(tk)
+        barrier()
+        t = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device="cuda")
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_reps.append(float(t.item()))
+        e2e_toks = seq if e2e_toks is None else e2e_toks
+        if sum(e2e_reps) >= MIN_TIMED_S or len(e2e_reps) >= 400:
+            break
+    e2e_s = st.median(e2e_reps)
     clocks = sampler.stop() if rank == 0 else None
-    same_tokens = list(toks) == e2e_toks
+    same_tokens = [int(t) for t in toks] == [int(t) for t in e2e_toks]
 
     # ---- roofline of the dominant kernel, timed alone with events on the same stream
     peak, peak_kind = measured_peak()
@@ -256,6 +316,30 @@ def run_ours(args, cfg):
         _, sms = model.decode_sampled(am, us)
         sampled = {"value": K / (sms * 1e-3), "unit": "tok/s", "steps": K,
                    "what": "decode step + top-p draw fed back on the device (nfai_decode_sampled)"}
+    # ---- the prompt path at a length where it is tensor-core bound: a 2 048-token pass of the same architecture
+    pf2048 = None
+    if world == 1 and cfg.dtype == "f16" and args.config == "c1" and not args.no_prefill_2048:
+        model.Dispose()
+        model = LlamaModel(factory.ctx, synth.metadata(cfg), synthetic_tensors(cfg, args.seed), 2048 + 8,
+                           kv_dtype=args.kv_dtype)
+        long_prompt = synth.prompt_ids(cfg, 2048, args.seed + 5)
+        model.prefill(long_prompt, want_logits=False)
+        times = []
+        for _ in range(5):
+            model.reset()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            model.prefill(long_prompt, want_logits=False)
+            torch.cuda.synchronize()
+            times.append(time.perf_counter() - t0)
+        tsec = st.median(times)
+        flops = (2.0 * (cfg.streamed_matrix_params() - cfg.V * cfg.H) * 2048 + 2.0 * 2048 * 2048 * cfg.qDim * cfg.L
+                 + 2.0 * cfg.V * cfg.H)
+        sus, burst, kind = measured_tflops()
+        pf2048 = {"tokens": 2048, "ms": tsec * 1e3, "tok_s": 2048 / tsec, "tflops": flops / tsec / 1e12,
+                  "frac_of_sustained_bf16": flops / tsec / 1e12 / sus, "frac_of_burst_bf16": flops / tsec / 1e12 / burst,
+                  "peak_kind": kind, "timing": "host clock around nfai_prefill with a synchronise on both sides, median of 5",
+                  "flops": "2 x layer matrix params x T + causal attention 2 T^2 qDim L + one LM-head row"}
     launches = model.step_launches()
     kv_bytes = 2 if model.kv_dtype == "f16" else 4
     first_pos = PROMPT_LEN + W
@@ -273,6 +357,9 @@ def run_ours(args, cfg):
     line = {
         "metric": "decode tok/s (batch 1)", "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "timed": {"reps": len(reps_ms), "device_s": sum(reps_ms) * 1e-3, "statistic": "median over reps of K steps",
+                  "min_ms_per_step": min(reps_ms) / K, "max_ms_per_step": max(reps_ms) / K, "e2e_reps": len(e2e_reps)},
+        "tp_parity" if world > 1 else "parity": parity,
         "dtype": "f32 accumulate over " + cfg.dtype + " weights", "data": "synthetic",
         "config": {"workload": workload_name(args.config, cfg, K), "weights": cfg.dtype, "kv_cache": model.kv_dtype,
                    "parallelism": f"tp{world}", "exchange": exchange, "l2": "inputs larger than L2: every step streams all weights "
@@ -282,7 +369,8 @@ def run_ours(args, cfg):
                 "same_tokens_as_device_loop": same_tokens},
         "gpu_launches": K * launches,
         "roofline": {"bound": "hbm", "kernel": "gemv_kernel (FFN gate/up + RMSNorm + SiLU*up)", "achieved": dom["gbs"],
-                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": NCU_TRAFFIC_BYTES.get((args.config, world)),
+                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": (NCU_TRAFFIC.get((args.config, world)) or {}).get("bytes"),
+                     "traffic_capture": (NCU_TRAFFIC.get((args.config, world)) or {}).get("capture"),
                      "launch_us": dom["us"], "bytes_per_launch": dom["bytes"]},
         "step_roofline": {"bytes_per_token_per_gpu": step_bytes, "achieved_gbs": step_bytes / (ms / K * 1e-3) / 1e9,
                           "frac_of_8tbs": step_bytes / (ms / K * 1e-3) / 8e12,
@@ -296,13 +384,22 @@ def run_ours(args, cfg):
                     "tflops": (2.0 * (cfg.streamed_matrix_params() - cfg.V * cfg.H) * PROMPT_LEN
                                + 2.0 * PROMPT_LEN * PROMPT_LEN * cfg.qDim * cfg.L) / prefill_s / 1e12},
     }
+    line["kernels"]["lm_head"]["note"] = ("timed alone the loop re-reads one matrix: the part of it that stays in the "
+                                          "126 MB L2 lifts this figure a few percent above the HBM copy peak")
+    if pf2048 is not None:
+        line["prefill_2048"] = pf2048
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         n_tok = 8
         v, s_per = cpu_baseline(cfg, threads, n_tok, args.seed)
+        v1, _ = cpu_baseline(cfg, 1, 2, args.seed)
         line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": threads, "kind": "port",
                                 "sample": f"{n_tok} decode steps at positions {PROMPT_LEN + 1}.. of the same model "
-                                          "(KV rows below are zero-filled), all host threads"}
+                                          "(KV rows below are zero-filled), all host threads",
+                                "one_thread": {"value": v1, "unit": "tok/s", "cores": 1, "sample": "2 decode steps"}}
+        line["vs_cpu_port"] = {"device_loop": value / v, "e2e": (K / e2e_s) / v,
+                               "note": "GPU over the CPU port of the reference's arithmetic on this box's host cores; "
+                                       "vs_baseline stays null: the reference publishes no number for this metric"}
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
@@ -319,6 +416,7 @@ def main():
     ap.add_argument("--kv-dtype", default="f16", choices=["f16", "f32", "auto"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-prefill-2048", action="store_true", help="skip the 2 048-token prompt measurement")
     ap.add_argument("--nccl-allreduce", action="store_true", help="N > 1: use NCCL all-reduces instead of the peer-memory kernel")
     ap.add_argument("--prompt-len", type=int, default=0,
                     help="0 = the configuration's own prompt length (c1 128, c2 2048, c3 1024, c4 32768)")

@@ -61,6 +61,7 @@ internal static unsafe partial class Native
     [DllImport(Lib)] internal static extern int nfai_set_position(IntPtr model, uint pos);
     [DllImport(Lib)] internal static extern int nfai_read_kv(IntPtr model, uint layer, uint pos, float* k, float* v);
     [DllImport(Lib)] internal static extern int nfai_write_kv(IntPtr model, uint layer, uint pos, float* k, float* v);
+    [DllImport(Lib)] internal static extern int nfai_write_kv_range(IntPtr model, uint layer, uint pos0, uint n, float* k, float* v);
     [DllImport(Lib)] internal static extern int nfai_read_hidden(IntPtr model, uint layer, float* outHidden);
     [DllImport(Lib)] internal static extern int nfai_model_tune(IntPtr model, int which, int mode, int rowsPerWarp, int depth, int ctasPerSm);
     [DllImport(Lib)] internal static extern int nfai_model_set_prefetch(IntPtr model, ulong lookaheadBytes, ulong extraBytes, int mode);

@@ -212,6 +212,9 @@ int nfai_read_kv(nfai_model* m, uint32_t layer, uint32_t pos, float* k, float* v
 
 /* Overwrite K and V rows of `layer` at `pos` from float32 host data (used to seed long-context tests). */
 int nfai_write_kv(nfai_model* m, uint32_t layer, uint32_t pos, const float* k, const float* v);
+/* The same for n consecutive positions starting at pos0 (k and v hold n rows of this rank's KV width): seeds a long
+ * cache for tests of long-context decoding without ingesting a long prompt. No counterpart in the reference. */
+int nfai_write_kv_range(nfai_model* m, uint32_t layer, uint32_t pos0, uint32_t n, const float* k, const float* v);
 
 /* Set the position without touching the cache (pairs with nfai_write_kv). */
 int nfai_set_position(nfai_model* m, uint32_t pos);
@@ -232,10 +235,13 @@ int nfai_profile_kernel(nfai_model* m, int which, int iters, float* avg_ms, uint
 /* Launch shape of one GEMV kernel of the decode step (selector as in nfai_profile_kernel, 0..4).
  * mode 0: weights double-buffered in registers; rows_per_warp in {1,2,4}, depth = 16-byte loads in flight per row
  *         per lane in {2,4,8}.
- * mode 1: weights staged through a shared-memory ring by bulk asynchronous copies; rows_per_warp in {1,2},
- *         depth = ring stages per warp in {2,3,4,6}.
+ * mode 1 / 2: weights staged through per-warp shared-memory rings by bulk asynchronous copies, stages of
+ *         2 rows x 2 KB / 2 rows x 4 KB; rows_per_warp = 2, depth = ring stages per warp in {1,2,3,4}.
  * The QKV and gate/up kernels need an even rows_per_warp. ctas_per_sm bounds the persistent grid. Results do not
  * depend on the shape. After nfai_model_finalize the decode graphs are captured again.
+ * Selector 5 switches how the kernels of a step hand over to each other: mode 1 (default) = a counter per kernel
+ * that the CTAs of the next kernel poll, mode 0 = every kernel waits for its predecessor to complete; the other
+ * arguments are ignored.
  * No counterpart in the reference (its dispatch sizes are fixed in each shader class). */
 int nfai_model_tune(nfai_model* m, int which, int mode, int rows_per_warp, int depth, int ctas_per_sm);
 

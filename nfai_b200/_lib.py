@@ -84,6 +84,7 @@ SIGNATURES = {
     "nfai_reset": (_i, [_vp]),
     "nfai_read_kv": (_i, [_vp, _u32, _u32, C.POINTER(_f), C.POINTER(_f)]),
     "nfai_write_kv": (_i, [_vp, _u32, _u32, C.POINTER(_f), C.POINTER(_f)]),
+    "nfai_write_kv_range": (_i, [_vp, _u32, _u32, _u32, C.POINTER(_f), C.POINTER(_f)]),
     "nfai_set_position": (_i, [_vp, _u32]),
     "nfai_read_hidden": (_i, [_vp, _u32, C.POINTER(_f)]),
     "nfai_profile_kernel": (_i, [_vp, _i, _i, C.POINTER(_f), C.POINTER(C.c_uint64)]),

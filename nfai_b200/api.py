@@ -242,6 +242,14 @@ class LlamaModel:
         v = np.ascontiguousarray(v, np.float32)
         check(self._lib.nfai_write_kv(self.handle, layer, pos, self._fp(k), self._fp(v)), self.ctx.handle)
 
+    def write_kv_range(self, layer: int, pos0: int, k: np.ndarray, v: np.ndarray):
+        """k, v: [n][kv width] rows for positions pos0 .. pos0+n-1 of one layer."""
+        k = np.ascontiguousarray(k, np.float32)
+        v = np.ascontiguousarray(v, np.float32)
+        assert k.shape == v.shape and k.ndim == 2 and k.shape[1] == self._kv_len()
+        check(self._lib.nfai_write_kv_range(self.handle, layer, pos0, k.shape[0], self._fp(k), self._fp(v)),
+              self.ctx.handle)
+
     def read_hidden(self, layer: int) -> np.ndarray:
         out = np.empty(self.H, np.float32)
         check(self._lib.nfai_read_hidden(self.handle, layer, self._fp(out)), self.ctx.handle)
@@ -260,6 +268,10 @@ class LlamaModel:
     def tune(self, which: str, mode: int, rows_per_warp: int, depth: int, ctas_per_sm: int):
         check(self._lib.nfai_model_tune(self.handle, self.KERNELS[which], mode, rows_per_warp, depth, ctas_per_sm),
               self.ctx.handle)
+
+    def set_links(self, on: bool):
+        """Hand-over between the kernels of a step: counters (True, default) or kernel-completion waits (False)."""
+        check(self._lib.nfai_model_tune(self.handle, 5, 1 if on else 0, 2, 4, 1), self.ctx.handle)
 
     def set_prefetch(self, lookahead_bytes: int, extra_bytes: int = 0, mode: int = 1):
         check(self._lib.nfai_model_set_prefetch(self.handle, int(lookahead_bytes), int(extra_bytes), mode),
@@ -325,19 +337,19 @@ class LlamaModelFactory:
 def synthetic_tensors(cfg, seed: int = 0) -> List[ComputeCollection]:
     """The seeded synthetic model as lazy in-memory ComputeCollections (no file)."""
     from . import synth
-    return [_LazySynth(cfg, name, ne, dt, seed) for name, ne, dt in synth.tensor_specs(cfg)]
+    src = synth.TensorSource(cfg, seed)
+    return [_LazySynth(src, name, ne, dt) for name, ne, dt in src.specs]
 
 
 class _LazySynth(ComputeCollection):
     """Generates its values when streamed, so a large model never sits in host memory twice."""
 
-    def __init__(self, cfg, name, ne, dt, seed):
+    def __init__(self, source, name, ne, dt):
         super().__init__(name, ne, 2 if dt == "f16" else 4)
-        self._cfg, self._ne, self._dt, self._seed = cfg, ne, dt, seed
+        self._source = source  # shared by the tensors of one model: generates a few tensors ahead on worker threads
 
     def get_data_raw(self, widen_half: bool = False):
-        from . import synth
-        self._array = synth.gen_tensor(self._cfg, self.Name, self._ne, self._dt, self._seed)
+        self._array = self._source.get(self.Name)
         try:
             yield from super().get_data_raw(widen_half=widen_half)
         finally:

@@ -137,6 +137,9 @@ struct nfai_model {
   uint32_t* prompt = nullptr;
   float* pin_logits = nullptr;  // pinned V floats
   float* tp_buf = nullptr;      // [H] partial sums exchanged between ranks
+  uint32_t* step_sync = nullptr;  // one hand-over counter per kernel of a step (StepLink)
+  uint32_t step_sync_words = 0;
+  bool use_links = true;
   void* sample_scratch = nullptr;  // per-slice sums and candidates of the on-device sampler
   cudaGraphExec_t g_full = nullptr, g_nohead = nullptr;
   int launches_full = 0;
@@ -399,22 +402,47 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     g.tp.push_index = index;
   };
   const bool pdl_x = pdl && (!tp_on || fused_x);  // a kernel that follows an NCCL call is launched plainly
+  // Hand-over counters instead of kernel-completion waits between the kernels of the step (StepLink); not with
+  // NCCL calls in the stream, which take no part in the counting.
+  const bool links = m->use_links && (!tp_on || fused_x);
+  uint32_t link_k = 0, prev_ctas = 0;
+  auto link_for = [&](uint32_t my_ctas, bool may_poll) {
+    StepLink lk;
+    lk.wait_ns = c->wait_ns;
+    if (!links) return lk;
+    lk.done = m->step_sync + link_k;
+    if (link_k > 0 && may_poll) {
+      lk.wait = m->step_sync + link_k - 1;
+      lk.target = prev_ctas;
+    }
+    ++link_k;
+    prev_ctas = my_ctas;
+    return lk;
+  };
   // the first kernel of a step must not overlap the previous step's tail: plain launch
   STEP(launch_embed(s, wdt, m->embd.ptr, hp.H, hp.V, m->state, from_prompt ? m->prompt : nullptr, 0, x_in(m, 0),
-                    pp.next(0, false), false));
+                    pp.next(0, false), false, links ? m->step_sync : nullptr, links ? m->step_sync_words : 0));
   for (uint32_t l = 0; l < hp.L; ++l) {
     const LayerW& LW = m->layers[l];
     GemvParams gq = qkv_params(m, l);
     gq.pf = pp.next(end_of(LW.qkv), true);
     if (l > 0) pull_into(gq, 2 * l - 1, x_mid(m, l - 1), x_in(m, l));
+    gq.link = link_for(gemv_grid(wdt, EPI_QKV_ROPE, gq, m->tune_qkv), true);
     STEP(launch_gemv(s, wdt, kvdt, EPI_QKV_ROPE, gq, m->tune_qkv, l > 0 ? pdl_x : pdl));
     AttnParams ga = attn_params(m, l);
     ga.pf = pp.next(end_of(LW.qkv), false);
-    if (!m->attn_maps.empty()) STEP(launch_attn_ring(s, ga, m->attn_maps[l], pdl));
-    else STEP(launch_attn_decode(s, kvdt, ga, pdl));
+    if (!m->attn_maps.empty()) {
+      // the tile-staged kernel reads K and V through the asynchronous proxy: it keeps the completion wait
+      ga.link = link_for(ga.kvH * attn_head_groups(ga.qH, ga.kvH, 4) * ga.S_max, false);
+      STEP(launch_attn_ring(s, ga, m->attn_maps[l], pdl));
+    } else {
+      ga.link = link_for(attn_decode_ctas(ga), true);
+      STEP(launch_attn_decode(s, kvdt, ga, pdl));
+    }
     GemvParams go = o_params(m, l);
     go.pf = pp.next(end_of(LW.o), true);
     push_from(go, 2 * l);
+    go.link = link_for(gemv_grid(wdt, EPI_STORE, go, m->tune_o), true);
     STEP(launch_gemv(s, wdt, kvdt, EPI_STORE, go, m->tune_o, pdl));
     if (tp_on && !fused_x) {
       e = tp_allreduce_residual(c->tp, s, m->tp_buf, x_in(m, l), x_mid(m, l), hp.H, &n);
@@ -423,10 +451,12 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     GemvParams gg = gateup_params(m, l);
     gg.pf = pp.next(end_of(LW.gateup), true);
     pull_into(gg, 2 * l, x_in(m, l), x_mid(m, l));
+    gg.link = link_for(gemv_grid(wdt, EPI_SILU_MUL, gg, m->tune_gateup), true);
     STEP(launch_gemv(s, wdt, kvdt, EPI_SILU_MUL, gg, m->tune_gateup, pdl_x));
     GemvParams gd = down_params(m, l);
     gd.pf = pp.next(pp.off(LW.ffn_norm.ptr) + (uint64_t)hp.H * 4, true);
     push_from(gd, 2 * l + 1);
+    gd.link = link_for(gemv_grid(wdt, EPI_STORE, gd, m->tune_down), true);
     STEP(launch_gemv(s, wdt, kvdt, EPI_STORE, gd, m->tune_down, pdl));
     if (tp_on && !fused_x) {
       e = tp_allreduce_residual(c->tp, s, m->tp_buf, x_mid(m, l), x_in(m, l + 1), hp.H, &n);
@@ -441,6 +471,7 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     pull_into(gh, 2 * hp.L - 1, x_mid(m, hp.L - 1), x_in(m, hp.L));
     push_from(gh, 2 * hp.L);
     gh.v_lo = m->v_lo;
+    gh.link = link_for(gemv_grid(wdt, EPI_LOGITS, gh, m->tune_head), true);
     STEP(launch_gemv(s, wdt, kvdt, EPI_LOGITS, gh, m->tune_head, pdl_x));
     if (tp_on && !fused_x) {
       e = tp_gather_argmax(c->tp, s, m->part_val, m->part_idx, m->nparts, m->v_lo, &n);
@@ -454,11 +485,11 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     }
     STEP(launch_argmax_final(s, m->part_val, m->part_idx, tp_on ? (uint32_t)c->world : m->nparts, m->state,
                              nullptr, m->history, hp.ctx, pp.next(pp.total(), false), tp_on ? tp_epoch_ptr(c->tp) : nullptr, per_step,
-                             fin, pdl_x));
+                             fin, pdl_x, link_for(1, true)));
   } else {
     // head-less prompt step under tensor parallelism: the last down projection's sum is pulled by nobody (the
     // next step starts from a fresh embedding row), which the protocol allows
-    STEP(launch_advance(s, m->state, tp_on ? tp_epoch_ptr(c->tp) : nullptr, per_step, pdl_x));
+    STEP(launch_advance(s, m->state, tp_on ? tp_epoch_ptr(c->tp) : nullptr, per_step, pdl_x, link_for(1, true)));
   }
 #undef STEP
   if (launches) *launches = n;
@@ -927,8 +958,10 @@ int nfai_model_finalize(nfai_model* m) {
   const size_t o_hi = take((size_t)hp.ctx * 4);
   const size_t o_pr = take((size_t)hp.ctx * 4);
   const size_t o_tp = take((size_t)hp.H * 4);
+  m->step_sync_words = 3 + 5 * hp.L + 5;
+  const size_t o_sy = take((size_t)m->step_sync_words * 4);
   // batched prompt workspace
-  const bool want_pf = hp.weight_dtype == NFAI_F16 && c->world == 1 && env_int("NFAI_PREFILL_GEMM", 1) != 0 &&
+  const bool want_pf = hp.weight_dtype == NFAI_F16 && env_int("NFAI_PREFILL_GEMM", 1) != 0 &&
                        hp.H % 8 == 0 && m->qDimL % 8 == 0 && m->Fl % 8 == 0;
   // tokens per pass of the batched prompt path: long passes amortise ~130 launches per pass and fill the GEMM grids
   uint32_t pf_want = (uint32_t)env_int("NFAI_PREFILL_CHUNK", 2048);
@@ -977,6 +1010,8 @@ int nfai_model_finalize(nfai_model* m) {
   m->history = (uint32_t*)(m->rarena + o_hi);
   m->prompt = (uint32_t*)(m->rarena + o_pr);
   m->tp_buf = (float*)(m->rarena + o_tp);
+  m->step_sync = (uint32_t*)(m->rarena + o_sy);
+  m->use_links = env_int("NFAI_LINK", 1) != 0;
   m->prefill_gemm = want_pf && pfc > 0;
   m->pf_chunk = pfc;
   m->pfX0 = (float*)(m->rarena + o_px0);
@@ -1106,19 +1141,25 @@ static int prefill_batched(nfai_model* m, const uint32_t* tokens, int n) {
       a.seq_imm = pos0 + 1; a.out_half = m->pfAO;
       if (attn_prefill_tc_supported(hp.d) && env_int("NFAI_PREFILL_ATTN", 1) != 0) CU(c, launch_attn_prefill_tc(s, kvdt, a, T));
       else CU(c, launch_attn_prefill(s, kvdt, a, T));
+      // Tensor parallel: the O and down GEMMs produce this rank's partial [T][H]; rank 0 adds the residual into its
+      // partial and one NCCL all-reduce per GEMM makes the sums (bit-identical on every rank).
+      const bool tp_on = c->world > 1;
+      const bool add_resid = !tp_on || c->rank == 0;
       GemmEpilogue eo;
-      eo.kind = GEMM_EPI_STORE; eo.out_f32 = m->pfX1; eo.resid = m->pfX0;
+      eo.kind = GEMM_EPI_STORE; eo.out_f32 = m->pfX1; eo.resid = add_resid ? m->pfX0 : nullptr;
       eo.scratch = m->pfPart; eo.scratch_floats = m->pfPartFloats;
       CU(c, launch_gemm_tc(s, m->pfAO, (const __half*)L.o.ptr, T, hp.H, m->qDimL, eo, err));
+      if (tp_on) CU(c, tp_allreduce(c->tp, s, m->pfX1, (size_t)T * hp.H));
       CU(c, launch_rmsnorm_to_half(s, m->pfX1, L.ffn_norm.ptr, hp.eps, T, hp.H, m->pfA));
       GemmEpilogue eg;
       eg.kind = GEMM_EPI_SILU_MUL; eg.out_f16 = m->pfH;
       eg.scratch = m->pfPart; eg.scratch_floats = m->pfPartFloats;
       CU(c, launch_gemm_tc(s, m->pfA, (const __half*)L.gateup.ptr, T, 2 * m->Fl, hp.H, eg, err));
       GemmEpilogue ed;
-      ed.kind = GEMM_EPI_STORE; ed.out_f32 = m->pfX0; ed.resid = m->pfX1;
+      ed.kind = GEMM_EPI_STORE; ed.out_f32 = m->pfX0; ed.resid = add_resid ? m->pfX1 : nullptr;
       ed.scratch = m->pfPart; ed.scratch_floats = m->pfPartFloats;
       CU(c, launch_gemm_tc(s, m->pfH, (const __half*)L.down.ptr, T, hp.H, m->Fl, ed, err));
+      if (tp_on) CU(c, tp_allreduce(c->tp, s, m->pfX0, (size_t)T * hp.H));
       if (last_chunk)  // the last token's residual stream after this block, where the taps and the LM head expect it
         CU(c, cudaMemcpyAsync(x_in(m, l + 1), m->pfX0 + (size_t)(T - 1) * hp.H, (size_t)hp.H * 4, cudaMemcpyDeviceToDevice, s));
     }
@@ -1128,9 +1169,32 @@ static int prefill_batched(nfai_model* m, const uint32_t* tokens, int n) {
   // LM head + arg-max for the last token; the finishing kernel advances the position by one
   int rc = set_state_word(m, offsetof(StepState, pos), pos0 - 1, 3);
   if (rc) return rc;
-  CU(c, launch_gemv(s, hp.weight_dtype, kvdt, EPI_LOGITS, head_params(m), m->tune_head, false));
-  CU(c, launch_argmax_final(s, m->part_val, m->part_idx, m->nparts, m->state, nullptr, m->history, hp.ctx, PrefetchPlan(),
-                            nullptr, 0, XchgHooks(), false));
+  GemvParams gh = head_params(m);
+  if (c->world == 1) {
+    CU(c, launch_gemv(s, hp.weight_dtype, kvdt, EPI_LOGITS, gh, m->tune_head, false));
+    CU(c, launch_argmax_final(s, m->part_val, m->part_idx, m->nparts, m->state, nullptr, m->history, hp.ctx, PrefetchPlan(),
+                              nullptr, 0, XchgHooks(), false));
+    return NFAI_OK;
+  }
+  // vocabulary-sharded head: the ranks' best (value, index) pairs are exchanged as in a decode step, counted as
+  // one exchange of this context
+  if (tp_push_ready(c->tp)) {
+    gh.tp = tp_hooks(c->tp);
+    gh.tp.push = 1;
+    gh.tp.push_index = 0;
+    gh.v_lo = m->v_lo;
+    CU(c, launch_gemv(s, hp.weight_dtype, kvdt, EPI_LOGITS, gh, m->tune_head, false));
+    XchgHooks fin = tp_hooks(c->tp);
+    fin.pull = 1;
+    fin.pull_index = 0;
+    CU(c, launch_argmax_final(s, m->part_val, m->part_idx, (uint32_t)c->world, m->state, nullptr, m->history, hp.ctx,
+                              PrefetchPlan(), tp_epoch_ptr(c->tp), 1, fin, false));
+  } else {
+    CU(c, launch_gemv(s, hp.weight_dtype, kvdt, EPI_LOGITS, gh, m->tune_head, false));
+    CU(c, tp_gather_argmax(c->tp, s, m->part_val, m->part_idx, m->nparts, m->v_lo, nullptr));
+    CU(c, launch_argmax_final(s, m->part_val, m->part_idx, (uint32_t)c->world, m->state, nullptr, m->history, hp.ctx,
+                              PrefetchPlan(), nullptr, 0, XchgHooks(), false));
+  }
   return NFAI_OK;
 }
 
@@ -1386,6 +1450,30 @@ static int kv_rw(nfai_model* m, uint32_t layer, uint32_t pos, float* k, float* v
 int nfai_read_kv(nfai_model* m, uint32_t layer, uint32_t pos, float* k, float* v) { return kv_rw(m, layer, pos, k, v, nullptr, nullptr); }
 int nfai_write_kv(nfai_model* m, uint32_t layer, uint32_t pos, const float* k, const float* v) { return kv_rw(m, layer, pos, nullptr, nullptr, k, v); }
 
+int nfai_write_kv_range(nfai_model* m, uint32_t layer, uint32_t pos0, uint32_t n, const float* k, const float* v) {
+  int rc = ready(m);
+  if (rc) return rc;
+  nfai_ctx* c = m->ctx;
+  if (!k || !v || !n || layer >= m->hp.L || pos0 >= m->hp.ctx || n > m->hp.ctx - pos0)
+    return fail(c, NFAI_ERR_ARG, "layer or position range out of bounds");
+  const size_t kvs = dtype_size(m->hp.kv_dtype);
+  const size_t nel = (size_t)n * m->kvDimL;
+  const size_t off = ((size_t)layer * kv_layer_elems(m) + (size_t)pos0 * m->kvDimL) * kvs;
+  CU(c, cudaStreamSynchronize(c->stream));
+  std::vector<uint16_t> tmp(m->hp.kv_dtype == NFAI_F16 ? nel : 0);
+  for (int which = 0; which < 2; ++which) {
+    char* dev = (char*)(which == 0 ? m->kc : m->vc) + off;
+    const float* inp = which == 0 ? k : v;
+    if (m->hp.kv_dtype == NFAI_F32) {
+      CU(c, cudaMemcpy(dev, inp, nel * 4, cudaMemcpyHostToDevice));
+    } else {
+      for (size_t i = 0; i < nel; ++i) tmp[i] = __half_as_ushort(__float2half_rn(inp[i]));
+      CU(c, cudaMemcpy(dev, tmp.data(), nel * 2, cudaMemcpyHostToDevice));
+    }
+  }
+  return NFAI_OK;
+}
+
 int nfai_read_hidden(nfai_model* m, uint32_t layer, float* out) {
   int rc = ready(m);
   if (rc) return rc;
@@ -1399,6 +1487,28 @@ int nfai_read_hidden(nfai_model* m, uint32_t layer, float* out) {
 int nfai_model_tune(nfai_model* m, int which, int mode, int rows_per_warp, int depth, int ctas_per_sm) {
   if (!m) return fail(nullptr, NFAI_ERR_ARG, "model is null");
   nfai_ctx* c = m->ctx;
+  if (which == 5) {
+    // how the kernels of a step hand over: 0 = each waits for its predecessor's completion, 1 = counters (StepLink)
+    if (mode != 0 && mode != 1) return fail(c, NFAI_ERR_ARG, "hand-over mode must be 0 or 1");
+    m->use_links = mode != 0;
+    if (!m->finalized || !c->use_graph) return NFAI_OK;
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaStreamSynchronize(c->stream));
+    cudaGraphExec_t gf = nullptr, gn = nullptr;
+    int launches = 0;
+    int rc = capture(m, true, false, &gf, &launches);
+    if (rc == NFAI_OK) rc = capture(m, false, true, &gn, nullptr);
+    if (rc != NFAI_OK) {
+      if (gf) cudaGraphExecDestroy(gf);
+      return rc;
+    }
+    cudaGraphExecDestroy(m->g_full);
+    cudaGraphExecDestroy(m->g_nohead);
+    m->g_full = gf;
+    m->g_nohead = gn;
+    m->launches_full = launches;
+    return NFAI_OK;
+  }
   GemvTune* t = which == 0 ? &m->tune_gateup : which == 1 ? &m->tune_down : which == 2 ? &m->tune_qkv
               : which == 3 ? &m->tune_o : which == 4 ? &m->tune_head : nullptr;
   if (!t) return fail(c, NFAI_ERR_ARG, "kernel selector must be 0..4");

@@ -176,11 +176,15 @@ __device__ __forceinline__ void attn_finish(const AttnParams& p, const uint32_t 
 
 // One CTA of NW warps: KV head / head group `bx`, split `s` of a sequence of `seq` positions. Every thread of the
 // CTA must call it (it uses block barriers); it returns early, uniformly, when the split is not active.
-// CG = true reads q, K and V with L2-only loads (needed when the caller wrote them earlier in the same kernel).
+// CG = true reads q, K and V with L2-only loads (needed when the caller wrote them earlier in the same kernel, or
+// when the kernel may have started before its producer stored them).
 // kG = query heads that share one pass over K and V (fewer heads, fewer registers).
-template <typename KVT, int D, int NW, bool CG, int kG, int UNR_ = 0>
-__device__ __forceinline__ void attn_core(const AttnParams& p, const uint32_t bx, const uint32_t s, const uint32_t seq,
-                                          const uint32_t min_chunk) {
+// `link` is how the CTA waits for the kernel that produced q and the newest K/V row (StepLink): the K and V rows of
+// all EARLIER positions were written by earlier steps, so the first batch of them is requested before that wait and
+// is in registers when q arrives. Returns false when the wait ran out of time.
+template <typename KVT, int D, int NW, bool CG, int kG, int UNR_ = 0, typename Link>
+__device__ __forceinline__ bool attn_core(const AttnParams& p, const uint32_t bx, const uint32_t s, const uint32_t seq,
+                                          const uint32_t min_chunk, const Link& link) {
   constexpr int kAT = NW * 32;
   constexpr int kAW = NW;
   constexpr int LPP = D / 8;    // lanes per position
@@ -200,9 +204,35 @@ __device__ __forceinline__ void attn_core(const AttnParams& p, const uint32_t bx
   chunk = chunk < min_chunk ? min_chunk : chunk;
   chunk = (chunk + 63) / 64 * 64;
   const uint32_t S_eff = (seq + chunk - 1) / chunk;
-  if (s >= S_eff) return;
+  if (s >= S_eff) return true;
   const uint32_t t0 = s * chunk;
   const uint32_t t1 = min(seq, t0 + chunk);
+  const uint32_t newest = seq - 1;  // the row the producing kernel of this step writes
+
+  const KVT* kc = reinterpret_cast<const KVT*>(p.kcache) + g * D + sub * 8;
+  const KVT* vc = reinterpret_cast<const KVT*>(p.vcache) + g * D + sub * 8;
+
+  // ---- first batch, requested ahead of the dependency
+  uint32_t base = t0 + warp * PPW;
+  typename KV8<KVT>::Raw kr[UNR], vr[UNR];
+  bool valid[UNR];
+#pragma unroll
+  for (int u = 0; u < UNR; ++u) {
+    const uint32_t t = base + u * (kAW * PPW) + grp;
+    valid[u] = t < t1;
+    const bool early = valid[u] && t != newest;
+    kr[u] = early ? KV8<KVT>::template ld<CG>(kc + (size_t)t * kvDim) : KV8<KVT>::zero();
+    vr[u] = early ? KV8<KVT>::template ld<CG>(vc + (size_t)t * kvDim) : KV8<KVT>::zero();
+  }
+  const bool link_ok = link_wait(link);
+#pragma unroll
+  for (int u = 0; u < UNR; ++u) {
+    const uint32_t t = base + u * (kAW * PPW) + grp;
+    if (valid[u] && t == newest) {
+      kr[u] = KV8<KVT>::template ld<CG>(kc + (size_t)t * kvDim);
+      vr[u] = KV8<KVT>::template ld<CG>(vc + (size_t)t * kvDim);
+    }
+  }
 
   // this lane's eight dims of the (up to) four query heads
   float q[kG][8];
@@ -228,19 +258,8 @@ __device__ __forceinline__ void attn_core(const AttnParams& p, const uint32_t bx
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[j][e] = 0.f;
   }
-  const KVT* kc = reinterpret_cast<const KVT*>(p.kcache) + g * D + sub * 8;
-  const KVT* vc = reinterpret_cast<const KVT*>(p.vcache) + g * D + sub * 8;
 
-  for (uint32_t base = t0 + warp * PPW; base < t1; base += kAW * PPW * UNR) {
-    typename KV8<KVT>::Raw kr[UNR], vr[UNR];
-    bool valid[UNR];
-#pragma unroll
-    for (int u = 0; u < UNR; ++u) {
-      const uint32_t t = base + u * (kAW * PPW) + grp;
-      valid[u] = t < t1;
-      kr[u] = valid[u] ? KV8<KVT>::template ld<CG>(kc + (size_t)t * kvDim) : KV8<KVT>::zero();
-      vr[u] = valid[u] ? KV8<KVT>::template ld<CG>(vc + (size_t)t * kvDim) : KV8<KVT>::zero();
-    }
+  while (base < t1) {
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
       if (base + u * (kAW * PPW) >= t1) break;  // warp-uniform
@@ -266,11 +285,27 @@ __device__ __forceinline__ void attn_core(const AttnParams& p, const uint32_t bx
         }
       }
     }
+    base += kAW * PPW * UNR;
+    if (base >= t1) break;
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const uint32_t t = base + u * (kAW * PPW) + grp;
+      valid[u] = t < t1;
+      kr[u] = valid[u] ? KV8<KVT>::template ld<CG>(kc + (size_t)t * kvDim) : KV8<KVT>::zero();
+      vr[u] = valid[u] ? KV8<KVT>::template ld<CG>(vc + (size_t)t * kvDim) : KV8<KVT>::zero();
+    }
   }
 
   attn_finish<D, NW, kG>(p, bx, s, S_eff, h0, nh, m, l, acc);
+  return link_ok;
 }
 
+// The same for callers whose inputs are complete when the kernel starts (the wait is the plain dependency wait).
+template <typename KVT, int D, int NW, bool CG, int kG, int UNR_ = 0>
+__device__ __forceinline__ void attn_core(const AttnParams& p, const uint32_t bx, const uint32_t s, const uint32_t seq,
+                                          const uint32_t min_chunk) {
+  attn_core<KVT, D, NW, CG, kG, UNR_>(p, bx, s, seq, min_chunk, StepLink());
+}
 
 }  // namespace attn_detail
 }  // namespace nfai

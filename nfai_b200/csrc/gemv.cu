@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
   load_gain(p, xs);
   prefetch_plan(p.pf, kPrefetchChunk);
   pdl_launch_dependents();
-  pdl_wait();
+  const bool link_ok = link_wait(p.link);
   // what the epilogue of the first item reads (residual / cos, sin of this position) travels with x
   uint32_t pos = 0;
   if constexpr (EPI == EPI_QKV_ROPE) pos = p.state ? p.state->pos : p.pos_imm;
@@ -165,6 +165,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
   }
   if constexpr (EPI == EPI_LOGITS) cta_argmax_partial(p, best_v, best_i, red);
   if constexpr (EPI == EPI_STORE) push_publish(p);
+  kernel_end(p, link_ok);
 }
 
 // Same contract for any K and any alignment (element loads); used when K is not a multiple of the vector width.
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(kThreads) gemv_scalar_kernel(const GemvParams 
   load_gain(p, xs);
   prefetch_plan(p.pf, kPrefetchChunk);
   pdl_launch_dependents();
-  pdl_wait();
+  const bool link_ok = link_wait(p.link);
   load_x(p, xs, red);
   float best_v = -INFINITY;
   uint32_t best_i = 0xffffffffu;
@@ -197,6 +198,7 @@ __global__ void __launch_bounds__(kThreads) gemv_scalar_kernel(const GemvParams 
   }
   if constexpr (EPI == EPI_LOGITS) cta_argmax_partial(p, best_v, best_i, red);
   if constexpr (EPI == EPI_STORE) push_publish(p);
+  kernel_end(p, link_ok);
 }
 
 template <typename K>

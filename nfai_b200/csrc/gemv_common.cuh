@@ -58,14 +58,14 @@ __device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* re
     pull_epoch = *p.tp.epoch_base + p.tp.pull_index + 1;
   }
   if (p.gain == nullptr) {
-    for (uint32_t i = tid; i < K; i += kThreads) xs[i] = pull ? pull_value(p, pull_epoch, pull_ok, i) : p.x[i];
+    for (uint32_t i = tid; i < K; i += kThreads) xs[i] = pull ? pull_value(p, pull_epoch, pull_ok, i) : __ldcg(p.x + i);
     __syncthreads();
     return;
   }
   const float* gs = xs + K;  // staged by load_gain() before the dependency wait
   float ss = 0.f;
   for (uint32_t i = tid; i < K; i += kThreads) {
-    float v = pull ? pull_value(p, pull_epoch, pull_ok, i) : p.x[i];
+    float v = pull ? pull_value(p, pull_epoch, pull_ok, i) : __ldcg(p.x + i);
     xs[i] = v;
     ss = fmaf(v, v, ss);
   }
@@ -78,6 +78,16 @@ __device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* re
   const float rms = sqrtf(__fdiv_rn(tot, (float)K) + p.eps);
   for (uint32_t i = tid; i < K; i += kThreads) xs[i] = __fmul_rn(__fdiv_rn(xs[i], rms), gs[i]);
   __syncthreads();
+}
+
+// Last thing every thread of a GEMV CTA does: report a hand-over that ran out of time, tell the next kernel that this
+// CTA's rows are stored, then the deferred wait for the predecessor's completion (StepLink).
+__device__ __forceinline__ void kernel_end(const GemvParams& p, bool link_ok) {
+  if (!link_ok && threadIdx.x == 0) {
+    if (p.state) atomicOr(&p.state->err, 4u);
+    if (p.err) atomicOr(p.err, 4u);
+  }
+  link_done(p.link);
 }
 
 // ---- tensor-parallel push: the finished row sums of this rank go into its slot on every rank ----------------------

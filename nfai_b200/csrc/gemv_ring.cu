@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(kThreads) gemv_ring_kernel(const GemvParams p)
   }
   load_gain(p, xs);
   pdl_launch_dependents();
-  pdl_wait();
+  const bool link_ok = link_wait(p.link);
   uint32_t pos = 0;
   if constexpr (EPI == EPI_QKV_ROPE) pos = p.state ? p.state->pos : p.pos_imm;
   load_x(p, xs, red);
@@ -220,6 +220,7 @@ __global__ void __launch_bounds__(kThreads) gemv_ring_kernel(const GemvParams p)
   }
   if constexpr (EPI == EPI_LOGITS) cta_argmax_partial(p, best_v, best_i, red);
   if constexpr (EPI == EPI_STORE) push_publish(p);
+  kernel_end(p, link_ok);
 }
 
 template <typename Kern>

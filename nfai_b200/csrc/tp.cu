@@ -201,6 +201,13 @@ cudaError_t tp_allreduce_residual(TpComm* tp, cudaStream_t s, float* buf, const 
   return cudaGetLastError();
 }
 
+// Sum of buf[0..n) over the ranks, in place (prompt passes: [tokens][H] floats, megabytes, where NCCL over NVLink
+// is the right tool). The result is bit-identical on every rank.
+cudaError_t tp_allreduce(TpComm* tp, cudaStream_t s, float* buf, size_t n) {
+  ncclResult_t r = g_nccl.AllReduce(buf, buf, n, ncclFloat, ncclSum, tp->comm, s);
+  return r == ncclSuccess ? cudaSuccess : cudaErrorUnknown;
+}
+
 bool tp_push_ready(const TpComm* tp) { return tp->push_ready; }
 
 // Hooks for the kernels of one step; the caller fills in pull / push and the exchange indices.

@@ -27,6 +27,9 @@ uint32_t* tp_epoch_ptr(TpComm* tp);
 cudaError_t tp_allreduce_residual(TpComm* tp, cudaStream_t s, float* buf, const float* resid, float* x_out, uint32_t H,
                                   int* launches);
 
+// In-place sum of buf[0..n) over the ranks with NCCL (the prompt path's [tokens][H] exchanges).
+cudaError_t tp_allreduce(TpComm* tp, cudaStream_t s, float* buf, size_t n);
+
 // After tp_import_peer_descs: the exchanges run inside the GEMV kernels (push in the epilogue of the producer, pull
 // in the prologue of the consumer; xchg_protocol.h). tp_hooks gives the view, epoch word, tickets and wait budget.
 bool tp_push_ready(const TpComm* tp);

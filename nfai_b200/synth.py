@@ -125,9 +125,47 @@ def gen_tensor(cfg: ModelConfig, name: str, shape_ne: Tuple[int, ...], dtype: st
     return a.astype(np.float16) if dtype == "f16" else a
 
 
+class TensorSource:
+    """Generates the tensors of one synthetic model a few ahead of the consumer, on worker threads.
+
+    Every tensor has its own random stream (seed, name), so the values do not depend on who generates them or in which
+    order; numpy fills large arrays without the interpreter lock, so the workers run in parallel. At most
+    `workers` tensors are held at a time."""
+
+    def __init__(self, cfg: ModelConfig, seed: int = 0, workers: int = 0):
+        import concurrent.futures as cf
+        import os
+        self.cfg, self.seed = cfg, seed
+        self.specs = list(tensor_specs(cfg))
+        self.index = {name: i for i, (name, _ne, _dt) in enumerate(self.specs)}
+        self.workers = workers or max(1, min(8, (os.cpu_count() or 2) - 1))
+        self.pool = cf.ThreadPoolExecutor(max_workers=self.workers)
+        self.futures = {}
+
+    def _submit(self, i: int):
+        if 0 <= i < len(self.specs) and i not in self.futures:
+            name, ne, dt = self.specs[i]
+            self.futures[i] = self.pool.submit(gen_tensor, self.cfg, name, ne, dt, self.seed)
+
+    def get(self, name: str) -> np.ndarray:
+        i = self.index[name]
+        self._submit(i)
+        for j in range(i + 1, i + 1 + self.workers):
+            self._submit(j)
+        return self.futures.pop(i).result()
+
+    def close(self):
+        self.pool.shutdown(wait=False, cancel_futures=True)
+        self.futures.clear()
+
+
 def iter_tensors(cfg: ModelConfig, seed: int = 0) -> Iterator[Tuple[str, Tuple[int, ...], str, np.ndarray]]:
-    for name, shape_ne, dtype in tensor_specs(cfg):
-        yield name, shape_ne, dtype, gen_tensor(cfg, name, shape_ne, dtype, seed)
+    src = TensorSource(cfg, seed)
+    try:
+        for name, shape_ne, dtype in src.specs:
+            yield name, shape_ne, dtype, src.get(name)
+    finally:
+        src.close()
 
 
 def prompt_ids(cfg: ModelConfig, n: int, seed: int = 0) -> np.ndarray:

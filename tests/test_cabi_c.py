@@ -36,6 +36,27 @@ def test_context_from_c(tmp_path):
     assert r.returncode == 0, (r.returncode, r.stdout, r.stderr)
 
 
+@pytest.mark.gpu
+def test_hot_path_from_plain_c(tmp_path):
+    """GGUF file -> native loader -> prompt -> greedy decode, all from a C program; the tokens must be the committed
+    golden ones of the tiny float32 configuration (prompt of 64, 64 greedy tokens)."""
+    import numpy as np
+
+    from nfai_b200 import gguf_io, synth
+    exe = _compile(tmp_path)
+    cfg = synth.get_config("c0")
+    gguf = str(tmp_path / "c0.gguf")
+    gguf_io.write_synthetic_gguf(cfg, gguf, seed=0)
+    gold = np.load(os.path.join(ROOT, "tests", "golden", "c0.npz"))
+    toks = str(tmp_path / "tokens.txt")
+    with open(toks, "w") as fh:
+        fh.write(" ".join(str(int(t)) for t in gold["prompt"]) + "\n")
+        fh.write(" ".join(str(int(t)) for t in gold["greedy"]) + "\n")
+    r = subprocess.run([exe, "gpu", gguf, toks], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, (r.returncode, r.stdout, r.stderr)
+    assert "hot path ok" in r.stdout
+
+
 def _compile_xchg_model(tmp_path):
     gxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else shutil.which("g++")
     if not gxx:

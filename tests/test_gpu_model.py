@@ -309,6 +309,57 @@ def test_full_size_1b_properties(factory, oracle):
     m.Dispose()
 
 
+@pytest.mark.parametrize("key", ["c2", "c3"])
+def test_full_size_3b_and_8b_against_the_oracle(factory, oracle, key):
+    """The 3B-architecture model (head_dim 128, 28 layers) and the 8B-architecture model (untied LM head, 32 layers)
+    at full size: three teacher-forced positions against the CPU oracle, float16 bound."""
+    cfg = synth.get_config(key)
+    m = make(cfg, 8, factory, kv_dtype="f16")
+    ref = oracle.OracleModel(cfg, ctx=8).load_synthetic(0)
+    toks = synth.prompt_ids(cfg, 3, 0)
+    worst = 0.0
+    for t in toks:
+        want = ref.decode(int(t))
+        got, am = m.decode(int(t))
+        worst = max(worst, float(np.abs(got - want).max()))
+        assert am == oracle.argmax(got)
+    assert worst <= ABS_F16, worst
+    # the batched prompt path over the same three tokens ends at the same logits
+    m.reset()
+    got, _ = m.prefill(toks)
+    assert float(np.abs(got - want).max()) <= ABS_F16
+    assert m.step_launches() == 3 + 5 * cfg.L
+    ref.close()
+    m.Dispose()
+
+
+def test_full_size_long_context_decode_against_the_oracle(factory, oracle):
+    """The long-context configuration at full size: the 1B-architecture model with a float16 cache seeded to 32 768
+    positions (random rows, the same on both sides; ingesting a 32 768-token prompt on the CPU would take an hour),
+    then two decode steps at positions 32 768 and 32 769 against the oracle."""
+    cfg = synth.get_config("c1")
+    n = 32768
+    m = make(cfg, n + 8, factory, kv_dtype="f16")
+    ref = oracle.OracleModel(cfg, ctx=n + 8).load_synthetic(0)
+    rng = np.random.default_rng(4)
+    for l in range(cfg.L):
+        k = (rng.standard_normal((n, cfg.kvDim), dtype=np.float32) * 0.5).astype(np.float16).astype(np.float32)
+        v = (rng.standard_normal((n, cfg.kvDim), dtype=np.float32) * 0.5).astype(np.float16).astype(np.float32)
+        m.write_kv_range(l, 0, k, v)
+        for p in range(n):
+            ref.write_kv(l, p, k[p], v[p])
+    m.set_position(n)
+    ref.set_position(n)
+    for t in synth.prompt_ids(cfg, 2, 3):
+        want = ref.decode(int(t))
+        got, am = m.decode(int(t))
+        assert np.isfinite(got).all()
+        assert float(np.abs(got - want).max()) <= ABS_F16
+        assert am == oracle.argmax(got)
+    ref.close()
+    m.Dispose()
+
+
 @pytest.mark.parametrize("key", ["s3", "s2"])
 def test_long_cache_attention_ignores_stale_rows(factory, oracle, monkeypatch, key):
     """A cache longer than 4096 positions selects the tile-staged attention kernel; rows past the sequence hold

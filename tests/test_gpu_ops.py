@@ -147,11 +147,13 @@ def test_ffn_gate_up(cuda_ctx, oracle, H, F, dtype):
 
 
 @pytest.mark.parametrize("qH,kvH,d", [(8, 2, 32), (4, 2, 64), (32, 8, 64), (24, 8, 128), (8, 1, 64), (5, 5, 32)])
-@pytest.mark.parametrize("seq", [1, 2, 31, 32, 33, 100, 700, 5000])
+@pytest.mark.parametrize("seq", [1, 2, 31, 32, 33, 100, 700, 5000, 32768])
 @pytest.mark.parametrize("kvdtype", [np.float32, np.float16])
 def test_attention_decode(cuda_ctx, oracle, qH, kvH, d, seq, kvdtype):
     if seq == 5000 and (qH, kvH, d) not in ((32, 8, 64), (8, 1, 64), (24, 8, 128)):
         pytest.skip("long sequences on three geometries only")
+    if seq == 32768 and (qH, kvH, d) != (32, 8, 64):
+        pytest.skip("the longest sequence on the long-context configuration's geometry only")
     rng = np.random.default_rng(seq * 31 + d)
     kvDim = kvH * d
     q = rng.standard_normal(qH * d).astype(np.float32)
@@ -228,11 +230,13 @@ def test_argmax_ties_pick_the_lowest_index(cuda_ctx, oracle):
 
 
 @pytest.mark.parametrize("qH,kvH,d", [(32, 8, 64), (24, 8, 128), (4, 2, 64), (8, 1, 64), (6, 2, 128)])
-@pytest.mark.parametrize("seq", [1, 2, 15, 16, 17, 100, 700, 5000, 20000])
+@pytest.mark.parametrize("seq", [1, 2, 15, 16, 17, 100, 700, 5000, 20000, 32768])
 def test_attention_tile_staged_kernel_every_length(cuda_ctx, oracle, monkeypatch, qH, kvH, d, seq):
     """The long-context kernel (K and V through shared-memory rings) forced on for every length of a float16 cache."""
     if seq == 20000 and (qH, kvH, d) not in ((32, 8, 64), (24, 8, 128)):
-        pytest.skip("the longest sequence on two geometries only")
+        pytest.skip("the longest sequences on few geometries only")
+    if seq == 32768 and (qH, kvH, d) != (32, 8, 64):
+        pytest.skip("the longest sequences on few geometries only")
     monkeypatch.setenv("NFAI_ATTN_RING", "1")
     rng = np.random.default_rng(seq * 17 + d + qH)
     kvDim = kvH * d

@@ -29,18 +29,29 @@ def _worker(rank: int, world: int, port: int, key: str, push: bool):
             tp.connect_peers(dist, factory.ctx)  # all-reduces through peer memory instead of NCCL
         model = LlamaModel(factory.ctx, synth.metadata(cfg), synthetic_tensors(cfg, 0), 48, kv_dtype="f32")
         ref = O.OracleModel(cfg, ctx=48).load_synthetic(0)
-        toks = synth.prompt_ids(cfg, 12, 0)
+        toks = synth.prompt_ids(cfg, 18, 0)
         worst = 0.0
-        for t in toks[:6]:
+
+        def err(got, want):  # the path's tolerances: relative for float32 models, absolute for float16 models
+            d = float(np.abs(got - want).max())
+            return d / float(np.abs(want).max()) if cfg.dtype == "f32" else d
+        for t in toks[:4]:
             want = ref.decode(int(t))
             got, am = model.decode(int(t))
             assert am == O.argmax(got)
-            worst = max(worst, float(np.abs(got - want).max() / np.abs(want).max()))
+            worst = max(worst, err(got, want))
+        # a short piece goes token by token, a longer one through the batched path (float16 models: sharded
+        # tensor-core GEMMs with one all-reduce of [tokens][H] after O and after down)
         want = None
-        for t in toks[6:]:
+        for t in toks[4:8]:
             want = ref.decode(int(t))
-        got, am = model.prefill(toks[6:])
-        worst = max(worst, float(np.abs(got - want).max() / np.abs(want).max()))
+        got, am = model.prefill(toks[4:8])
+        worst = max(worst, err(got, want))
+        for t in toks[8:]:
+            want = ref.decode(int(t))
+        got, am = model.prefill(toks[8:])
+        worst = max(worst, err(got, want))
+        assert am == O.argmax(got)
         greedy, _ = model.decode_greedy(am, 8)
         tk, exp = am, []
         for _ in range(8):
@@ -63,7 +74,7 @@ def test_tensor_parallel_matches_oracle(world, key, push):
     res = run_ranks(_worker, world, (key, push), timeout=300, port_base=29700 + (3 if push else 0))
     res.sort()
     for rank, worst, greedy, exp, dtype in res:
-        assert worst <= (1e-4 if dtype == "f32" else 2e-3), (rank, worst)
+        assert worst <= (1e-4 if dtype == "f32" else 2e-2), (rank, worst)
         assert greedy == res[0][2]          # every rank generated the same tokens
         if dtype == "f32":
             assert greedy == exp
