@@ -236,12 +236,11 @@ int nfai_profile_kernel(nfai_model* m, int which, int iters, float* avg_ms, uint
  * mode 0: weights double-buffered in registers; rows_per_warp in {1,2,4}, depth = 16-byte loads in flight per row
  *         per lane in {2,4,8}.
  * mode 1 / 2: weights staged through per-warp shared-memory rings by bulk asynchronous copies, stages of
- *         2 rows x 2 KB / 2 rows x 4 KB; rows_per_warp = 2, depth = ring stages per warp in {1,2,3,4}.
+ *         2 rows x 2 KB / 2 rows x 4 KB; rows_per_warp = 2, depth = ring stages per warp in {1,2,3,4}, plus
+ *         8 x the number of further stages per warp that are requested into L2 while the kernel waits for its input.
  * The QKV and gate/up kernels need an even rows_per_warp. ctas_per_sm bounds the persistent grid. Results do not
  * depend on the shape. After nfai_model_finalize the decode graphs are captured again.
- * Selector 5 switches how the kernels of a step hand over to each other: mode 1 (default) = a counter per kernel
- * that the CTAs of the next kernel poll, mode 0 = every kernel waits for its predecessor to complete; the other
- * arguments are ignored.
+
  * No counterpart in the reference (its dispatch sizes are fixed in each shader class). */
 int nfai_model_tune(nfai_model* m, int which, int mode, int rows_per_warp, int depth, int ctas_per_sm);
 

@@ -269,10 +269,6 @@ class LlamaModel:
         check(self._lib.nfai_model_tune(self.handle, self.KERNELS[which], mode, rows_per_warp, depth, ctas_per_sm),
               self.ctx.handle)
 
-    def set_links(self, on: bool):
-        """Hand-over between the kernels of a step: counters (True, default) or kernel-completion waits (False)."""
-        check(self._lib.nfai_model_tune(self.handle, 5, 1 if on else 0, 2, 4, 1), self.ctx.handle)
-
     def set_prefetch(self, lookahead_bytes: int, extra_bytes: int = 0, mode: int = 1):
         check(self._lib.nfai_model_set_prefetch(self.handle, int(lookahead_bytes), int(extra_bytes), mode),
               self.ctx.handle)

@@ -137,9 +137,6 @@ struct nfai_model {
   uint32_t* prompt = nullptr;
   float* pin_logits = nullptr;  // pinned V floats
   float* tp_buf = nullptr;      // [H] partial sums exchanged between ranks
-  uint32_t* step_sync = nullptr;  // one hand-over counter per kernel of a step (StepLink)
-  uint32_t step_sync_words = 0;
-  bool use_links = true;
   void* sample_scratch = nullptr;  // per-slice sums and candidates of the on-device sampler
   cudaGraphExec_t g_full = nullptr, g_nohead = nullptr;
   int launches_full = 0;
@@ -185,14 +182,15 @@ void read_tune(const char* name, GemvTune& t, int r_default, int u_default) {
   std::string key = std::string("NFAI_TUNE_") + name;
   const char* v = getenv(key.c_str());
   if (v) {
-    int r = 0, u = 0, cps = 0, mode = 0, split = 0;
-    int got = sscanf(v, "%d,%d,%d,%d,%d", &r, &u, &cps, &mode, &split);
+    int r = 0, u = 0, cps = 0, mode = 0, split = 0, ahead = 0;
+    int got = sscanf(v, "%d,%d,%d,%d,%d,%d", &r, &u, &cps, &mode, &split, &ahead);
     if (got >= 2 && (r == 1 || r == 2 || r == 4) && (u == 1 || u == 2 || u == 3 || u == 4 || u == 8)) {
       t.rows_per_warp = r;
       t.unroll = u;
       if (got >= 3 && cps >= 1 && cps <= 16) t.ctas_per_sm = cps;
       if (got >= 4 && (mode == 0 || mode == 1 || mode == 2)) t.mode = mode;
       if (got >= 5 && (split == 0 || split == 1 || split == 2 || split == 4 || split == 8)) t.split = split;
+      if (got >= 6 && ahead >= 0 && ahead <= 64) t.l2_ahead = ahead;
     }
   }
 }
@@ -380,7 +378,7 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
   // LM head, pull in the prologue of the kernel that consumes the sum), so the step has the same launches as on one
   // GPU. Without peer memory: NCCL all-reduce + residual-add kernel after O and down, pair gather after the LM head.
   const bool tp_on = c->world > 1;
-  const bool fused_x = tp_on && tp_push_ready(c->tp);
+  const bool fused_x = tp_on && tp_push_ready(c->tp) && hp.H % 4 == 0 && hp.H <= xchg::kMaxH;
   const XchgHooks hooks = fused_x ? tp_hooks(c->tp) : XchgHooks();
   auto pull_into = [&](GemvParams& g, uint32_t index, const float* resid, float* store) {
     if (!fused_x) return;
@@ -402,47 +400,22 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     g.tp.push_index = index;
   };
   const bool pdl_x = pdl && (!tp_on || fused_x);  // a kernel that follows an NCCL call is launched plainly
-  // Hand-over counters instead of kernel-completion waits between the kernels of the step (StepLink); not with
-  // NCCL calls in the stream, which take no part in the counting.
-  const bool links = m->use_links && (!tp_on || fused_x);
-  uint32_t link_k = 0, prev_ctas = 0;
-  auto link_for = [&](uint32_t my_ctas, bool may_poll) {
-    StepLink lk;
-    lk.wait_ns = c->wait_ns;
-    if (!links) return lk;
-    lk.done = m->step_sync + link_k;
-    if (link_k > 0 && may_poll) {
-      lk.wait = m->step_sync + link_k - 1;
-      lk.target = prev_ctas;
-    }
-    ++link_k;
-    prev_ctas = my_ctas;
-    return lk;
-  };
   // the first kernel of a step must not overlap the previous step's tail: plain launch
   STEP(launch_embed(s, wdt, m->embd.ptr, hp.H, hp.V, m->state, from_prompt ? m->prompt : nullptr, 0, x_in(m, 0),
-                    pp.next(0, false), false, links ? m->step_sync : nullptr, links ? m->step_sync_words : 0));
+                    pp.next(0, false), false));
   for (uint32_t l = 0; l < hp.L; ++l) {
     const LayerW& LW = m->layers[l];
     GemvParams gq = qkv_params(m, l);
     gq.pf = pp.next(end_of(LW.qkv), true);
     if (l > 0) pull_into(gq, 2 * l - 1, x_mid(m, l - 1), x_in(m, l));
-    gq.link = link_for(gemv_grid(wdt, EPI_QKV_ROPE, gq, m->tune_qkv), true);
     STEP(launch_gemv(s, wdt, kvdt, EPI_QKV_ROPE, gq, m->tune_qkv, l > 0 ? pdl_x : pdl));
     AttnParams ga = attn_params(m, l);
     ga.pf = pp.next(end_of(LW.qkv), false);
-    if (!m->attn_maps.empty()) {
-      // the tile-staged kernel reads K and V through the asynchronous proxy: it keeps the completion wait
-      ga.link = link_for(ga.kvH * attn_head_groups(ga.qH, ga.kvH, 4) * ga.S_max, false);
-      STEP(launch_attn_ring(s, ga, m->attn_maps[l], pdl));
-    } else {
-      ga.link = link_for(attn_decode_ctas(ga), true);
-      STEP(launch_attn_decode(s, kvdt, ga, pdl));
-    }
+    if (!m->attn_maps.empty()) STEP(launch_attn_ring(s, ga, m->attn_maps[l], pdl));
+    else STEP(launch_attn_decode(s, kvdt, ga, pdl));
     GemvParams go = o_params(m, l);
     go.pf = pp.next(end_of(LW.o), true);
     push_from(go, 2 * l);
-    go.link = link_for(gemv_grid(wdt, EPI_STORE, go, m->tune_o), true);
     STEP(launch_gemv(s, wdt, kvdt, EPI_STORE, go, m->tune_o, pdl));
     if (tp_on && !fused_x) {
       e = tp_allreduce_residual(c->tp, s, m->tp_buf, x_in(m, l), x_mid(m, l), hp.H, &n);
@@ -451,12 +424,10 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     GemvParams gg = gateup_params(m, l);
     gg.pf = pp.next(end_of(LW.gateup), true);
     pull_into(gg, 2 * l, x_in(m, l), x_mid(m, l));
-    gg.link = link_for(gemv_grid(wdt, EPI_SILU_MUL, gg, m->tune_gateup), true);
     STEP(launch_gemv(s, wdt, kvdt, EPI_SILU_MUL, gg, m->tune_gateup, pdl_x));
     GemvParams gd = down_params(m, l);
     gd.pf = pp.next(pp.off(LW.ffn_norm.ptr) + (uint64_t)hp.H * 4, true);
     push_from(gd, 2 * l + 1);
-    gd.link = link_for(gemv_grid(wdt, EPI_STORE, gd, m->tune_down), true);
     STEP(launch_gemv(s, wdt, kvdt, EPI_STORE, gd, m->tune_down, pdl));
     if (tp_on && !fused_x) {
       e = tp_allreduce_residual(c->tp, s, m->tp_buf, x_mid(m, l), x_in(m, l + 1), hp.H, &n);
@@ -471,7 +442,6 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     pull_into(gh, 2 * hp.L - 1, x_mid(m, hp.L - 1), x_in(m, hp.L));
     push_from(gh, 2 * hp.L);
     gh.v_lo = m->v_lo;
-    gh.link = link_for(gemv_grid(wdt, EPI_LOGITS, gh, m->tune_head), true);
     STEP(launch_gemv(s, wdt, kvdt, EPI_LOGITS, gh, m->tune_head, pdl_x));
     if (tp_on && !fused_x) {
       e = tp_gather_argmax(c->tp, s, m->part_val, m->part_idx, m->nparts, m->v_lo, &n);
@@ -485,11 +455,11 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     }
     STEP(launch_argmax_final(s, m->part_val, m->part_idx, tp_on ? (uint32_t)c->world : m->nparts, m->state,
                              nullptr, m->history, hp.ctx, pp.next(pp.total(), false), tp_on ? tp_epoch_ptr(c->tp) : nullptr, per_step,
-                             fin, pdl_x, link_for(1, true)));
+                             fin, pdl_x));
   } else {
     // head-less prompt step under tensor parallelism: the last down projection's sum is pulled by nobody (the
     // next step starts from a fresh embedding row), which the protocol allows
-    STEP(launch_advance(s, m->state, tp_on ? tp_epoch_ptr(c->tp) : nullptr, per_step, pdl_x, link_for(1, true)));
+    STEP(launch_advance(s, m->state, tp_on ? tp_epoch_ptr(c->tp) : nullptr, per_step, pdl_x));
   }
 #undef STEP
   if (launches) *launches = n;
@@ -958,8 +928,6 @@ int nfai_model_finalize(nfai_model* m) {
   const size_t o_hi = take((size_t)hp.ctx * 4);
   const size_t o_pr = take((size_t)hp.ctx * 4);
   const size_t o_tp = take((size_t)hp.H * 4);
-  m->step_sync_words = 3 + 5 * hp.L + 5;
-  const size_t o_sy = take((size_t)m->step_sync_words * 4);
   // batched prompt workspace
   const bool want_pf = hp.weight_dtype == NFAI_F16 && env_int("NFAI_PREFILL_GEMM", 1) != 0 &&
                        hp.H % 8 == 0 && m->qDimL % 8 == 0 && m->Fl % 8 == 0;
@@ -1010,8 +978,6 @@ int nfai_model_finalize(nfai_model* m) {
   m->history = (uint32_t*)(m->rarena + o_hi);
   m->prompt = (uint32_t*)(m->rarena + o_pr);
   m->tp_buf = (float*)(m->rarena + o_tp);
-  m->step_sync = (uint32_t*)(m->rarena + o_sy);
-  m->use_links = env_int("NFAI_LINK", 1) != 0;
   m->prefill_gemm = want_pf && pfc > 0;
   m->pf_chunk = pfc;
   m->pfX0 = (float*)(m->rarena + o_px0);
@@ -1487,28 +1453,6 @@ int nfai_read_hidden(nfai_model* m, uint32_t layer, float* out) {
 int nfai_model_tune(nfai_model* m, int which, int mode, int rows_per_warp, int depth, int ctas_per_sm) {
   if (!m) return fail(nullptr, NFAI_ERR_ARG, "model is null");
   nfai_ctx* c = m->ctx;
-  if (which == 5) {
-    // how the kernels of a step hand over: 0 = each waits for its predecessor's completion, 1 = counters (StepLink)
-    if (mode != 0 && mode != 1) return fail(c, NFAI_ERR_ARG, "hand-over mode must be 0 or 1");
-    m->use_links = mode != 0;
-    if (!m->finalized || !c->use_graph) return NFAI_OK;
-    CU(c, cudaSetDevice(c->device));
-    CU(c, cudaStreamSynchronize(c->stream));
-    cudaGraphExec_t gf = nullptr, gn = nullptr;
-    int launches = 0;
-    int rc = capture(m, true, false, &gf, &launches);
-    if (rc == NFAI_OK) rc = capture(m, false, true, &gn, nullptr);
-    if (rc != NFAI_OK) {
-      if (gf) cudaGraphExecDestroy(gf);
-      return rc;
-    }
-    cudaGraphExecDestroy(m->g_full);
-    cudaGraphExecDestroy(m->g_nohead);
-    m->g_full = gf;
-    m->g_nohead = gn;
-    m->launches_full = launches;
-    return NFAI_OK;
-  }
   GemvTune* t = which == 0 ? &m->tune_gateup : which == 1 ? &m->tune_down : which == 2 ? &m->tune_qkv
               : which == 3 ? &m->tune_o : which == 4 ? &m->tune_head : nullptr;
   if (!t) return fail(c, NFAI_ERR_ARG, "kernel selector must be 0..4");
@@ -1518,12 +1462,13 @@ int nfai_model_tune(nfai_model* m, int which, int mode, int rows_per_warp, int d
     ok = ok && (rows_per_warp == 1 || rows_per_warp == 2 || rows_per_warp == 4) && (depth == 2 || depth == 4 || depth == 8) &&
          rows_per_warp * depth <= 16;
   else
-    ok = ok && rows_per_warp == 2 && depth >= 1 && depth <= 4;
+    ok = ok && rows_per_warp == 2 && (depth & 7) >= 1 && (depth & 7) <= 4 && (depth >> 3) <= 64;
   if (!ok) return fail(c, NFAI_ERR_ARG, "unsupported launch shape");
   GemvTune old = *t;
   t->mode = mode;
   t->rows_per_warp = rows_per_warp;
-  t->unroll = depth;
+  t->unroll = mode == 0 ? depth : (depth & 7);
+  t->l2_ahead = mode == 0 ? 0 : (depth >> 3);
   t->ctas_per_sm = ctas_per_sm;
   if (!m->finalized) return NFAI_OK;
   CU(c, cudaSetDevice(c->device));
@@ -1840,7 +1785,8 @@ int nfai_op_gemv_xchg(nfai_ctx* c, const void* W, int dtype, uint32_t N, uint32_
   int rc = op_begin(c);
   if (rc) return rc;
   if (!W || bad_dtype(dtype) || !N || !K || (!pull_epoch && !x) || (!push_epoch && !y)) return fail(c, NFAI_ERR_ARG, "bad argument");
-  if (pull_epoch && (!pull_resid || !pull_store || K > xchg::kMaxH)) return fail(c, NFAI_ERR_ARG, "pull needs a residual, a store and K <= 16384");
+  if (pull_epoch && (!pull_resid || !pull_store || K > xchg::kMaxH || (K & 3) || (((uintptr_t)pull_resid | (uintptr_t)pull_store) & 15)))
+    return fail(c, NFAI_ERR_ARG, "pull needs a 16-byte aligned residual and store, K a multiple of 4 and K <= 16384");
   if (push_epoch && N > xchg::kMaxH) return fail(c, NFAI_ERR_ARG, "push needs N <= 16384");
   GemvParams p;
   p.W = W; p.N = N; p.K = K; p.x = x; p.gain = gain; p.eps = eps; p.y = y;

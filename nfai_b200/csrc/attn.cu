@@ -36,15 +36,13 @@ template <typename KVT, int D, int GH>
 __global__ void __launch_bounds__(kAT, 1) attn_decode_kernel(const AttnParams p) {
   prefetch_plan(p.pf, kPrefetchChunk);
   pdl_launch_dependents();
-  // q and the newest K/V row come from the previous kernel of this step (the wait for it is inside attn_core, after
-  // the earlier rows have been requested). The position was advanced by the previous STEP's last kernel, which has
-  // completed. The kernel may start before its producer has stored: q, K and V are read with L2 loads.
+  // q and the newest K/V row come from the previous kernel of this step: the wait for it is inside attn_core, after
+  // the earlier rows (written by earlier steps) have been requested. The position was advanced by the previous
+  // STEP's last kernel, which has completed. K and V are read with L2 loads: a line fetched before the wait must not
+  // serve a later read of the newest row from L1.
   const uint32_t seq = p.state ? p.state->pos + 1 : p.seq_imm;
   // one head per CTA leaves registers for eight steps of K and V in flight
-  const bool link_ok = attn_core<KVT, D, kAW, true, GH, (GH == 1 ? 2 * KV8<KVT>::kUnroll : 0)>(
-      p, blockIdx.x, blockIdx.y, seq, p.min_chunk, p.link);
-  if (!link_ok && threadIdx.x == 0 && p.state) atomicOr(&p.state->err, 4u);
-  link_done(p.link);
+  attn_core<KVT, D, kAW, true, GH, (GH == 1 ? 2 * KV8<KVT>::kUnroll : 0)>(p, blockIdx.x, blockIdx.y, seq, p.min_chunk);
 }
 
 // Prompt path: blockIdx.y is the token of the chunk; its sequence is one longer than the previous token's.
@@ -129,8 +127,6 @@ uint32_t attn_splits(uint32_t qH, uint32_t kvH, uint32_t max_seq, uint32_t heads
   uint32_t s = by_len < by_sm ? by_len : by_sm;
   return s < 1 ? 1 : s;
 }
-
-uint32_t attn_decode_ctas(const AttnParams& p) { return p.kvH * attn_head_groups(p.qH, p.kvH, p.heads_per_cta) * p.S_max; }
 
 size_t attn_part_floats(uint32_t qH, uint32_t d, uint32_t S_max) { return (size_t)qH * S_max * (d + 2); }
 

@@ -179,12 +179,12 @@ __device__ __forceinline__ void attn_finish(const AttnParams& p, const uint32_t 
 // CG = true reads q, K and V with L2-only loads (needed when the caller wrote them earlier in the same kernel, or
 // when the kernel may have started before its producer stored them).
 // kG = query heads that share one pass over K and V (fewer heads, fewer registers).
-// `link` is how the CTA waits for the kernel that produced q and the newest K/V row (StepLink): the K and V rows of
-// all EARLIER positions were written by earlier steps, so the first batch of them is requested before that wait and
-// is in registers when q arrives. Returns false when the wait ran out of time.
-template <typename KVT, int D, int NW, bool CG, int kG, int UNR_ = 0, typename Link>
-__device__ __forceinline__ bool attn_core(const AttnParams& p, const uint32_t bx, const uint32_t s, const uint32_t seq,
-                                          const uint32_t min_chunk, const Link& link) {
+// The CTA itself waits for the kernel that produced q and the newest K/V row (programmatic dependency wait): the K
+// and V rows of all EARLIER positions were written by earlier steps, so the first batch of them is requested before
+// that wait and is in registers when q arrives.
+template <typename KVT, int D, int NW, bool CG, int kG, int UNR_ = 0>
+__device__ __forceinline__ void attn_core(const AttnParams& p, const uint32_t bx, const uint32_t s, const uint32_t seq,
+                                          const uint32_t min_chunk) {
   constexpr int kAT = NW * 32;
   constexpr int kAW = NW;
   constexpr int LPP = D / 8;    // lanes per position
@@ -204,7 +204,7 @@ __device__ __forceinline__ bool attn_core(const AttnParams& p, const uint32_t bx
   chunk = chunk < min_chunk ? min_chunk : chunk;
   chunk = (chunk + 63) / 64 * 64;
   const uint32_t S_eff = (seq + chunk - 1) / chunk;
-  if (s >= S_eff) return true;
+  if (s >= S_eff) return;
   const uint32_t t0 = s * chunk;
   const uint32_t t1 = min(seq, t0 + chunk);
   const uint32_t newest = seq - 1;  // the row the producing kernel of this step writes
@@ -224,7 +224,7 @@ __device__ __forceinline__ bool attn_core(const AttnParams& p, const uint32_t bx
     kr[u] = early ? KV8<KVT>::template ld<CG>(kc + (size_t)t * kvDim) : KV8<KVT>::zero();
     vr[u] = early ? KV8<KVT>::template ld<CG>(vc + (size_t)t * kvDim) : KV8<KVT>::zero();
   }
-  const bool link_ok = link_wait(link);
+  pdl_wait();
 #pragma unroll
   for (int u = 0; u < UNR; ++u) {
     const uint32_t t = base + u * (kAW * PPW) + grp;
@@ -297,14 +297,6 @@ __device__ __forceinline__ bool attn_core(const AttnParams& p, const uint32_t bx
   }
 
   attn_finish<D, NW, kG>(p, bx, s, S_eff, h0, nh, m, l, acc);
-  return link_ok;
-}
-
-// The same for callers whose inputs are complete when the kernel starts (the wait is the plain dependency wait).
-template <typename KVT, int D, int NW, bool CG, int kG, int UNR_ = 0>
-__device__ __forceinline__ void attn_core(const AttnParams& p, const uint32_t bx, const uint32_t s, const uint32_t seq,
-                                          const uint32_t min_chunk) {
-  attn_core<KVT, D, NW, CG, kG, UNR_>(p, bx, s, seq, min_chunk, StepLink());
 }
 
 }  // namespace attn_detail

@@ -116,10 +116,7 @@ __global__ void __launch_bounds__(kRT, 1) attn_ring_kernel(const AttnParams p, c
   chunk = chunk < p.min_chunk ? p.min_chunk : chunk;
   chunk = (chunk + 63) / 64 * 64;
   const uint32_t S_eff = (seq + chunk - 1) / chunk;
-  if (s >= S_eff) {  // the whole CTA: nothing is in flight yet
-    link_done(p.link);
-    return;
-  }
+  if (s >= S_eff) return;  // the whole CTA: nothing is in flight yet
   const uint32_t t0 = s * chunk;
   const uint32_t t1 = min(seq, t0 + chunk);
   const uint32_t nblk = (t1 - t0 + PPS - 1) / PPS;
@@ -252,7 +249,6 @@ __global__ void __launch_bounds__(kRT, 1) attn_ring_kernel(const AttnParams p, c
 #pragma unroll
   for (int j = 0; j < kG; ++j) m[j] *= 0.6931471805599453f;
   attn_finish<D, kRW, kG>(p, bx, s, S_eff, h0, nh, m, l, acc);
-  link_done(p.link);  // this kernel waits for its predecessor's completion itself; the next one may poll its counter
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,

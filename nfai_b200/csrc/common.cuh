@@ -62,49 +62,6 @@ struct DeviceXchgMem {
   __device__ __forceinline__ unsigned long long now_ns() { return global_timer_ns(); }
 };
 
-// ---- hand-over between the kernels of one decode step (StepLink in kernels.h) -------------------------------------
-// Consumer side, called by every thread of the CTA where griddepcontrol.wait used to stand. Returns false when the
-// producer's counter did not reach the target within the budget (the caller raises error bit 4 and carries on).
-template <typename Link>
-__device__ __forceinline__ bool link_wait(const Link& link) {
-  if (link.wait == nullptr) {
-    pdl_wait();
-    return true;
-  }
-  __shared__ uint32_t s_link_ok;
-  if (threadIdx.x == 0) {
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(link.wait) : "memory");
-    uint32_t ok = 1;
-    if (v < link.target) {
-      const unsigned long long t0 = global_timer_ns();
-      uint32_t polls = 0;
-      while (true) {
-        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(link.wait) : "memory");
-        if (v >= link.target) break;
-        if ((++polls & 31u) == 0 && global_timer_ns() - t0 > link.wait_ns) {
-          ok = 0;
-          break;
-        }
-      }
-    }
-    s_link_ok = ok;
-  }
-  __syncthreads();
-  return s_link_ok != 0;
-}
-
-// Producer side, called by every thread of the CTA after its last store: one release-add per CTA, then the deferred
-// griddepcontrol.wait that keeps kernel completion ordered.
-template <typename Link>
-__device__ __forceinline__ void link_done(const Link& link) {
-  if (link.done != nullptr) {
-    __syncthreads();
-    if (threadIdx.x == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(link.done) : "memory");
-  }
-  if (link.wait != nullptr) pdl_wait();
-}
-
 // Ask the L2 for [ptr, ptr+bytes) of both ranges of a plan, the work split over every thread of the grid.
 // Nothing waits for the data: it is a hint that keeps HBM busy for the kernels that follow.
 template <typename Plan>

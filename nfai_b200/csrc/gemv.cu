@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
   load_gain(p, xs);
   prefetch_plan(p.pf, kPrefetchChunk);
   pdl_launch_dependents();
-  const bool link_ok = link_wait(p.link);
+  pdl_wait();
   // what the epilogue of the first item reads (residual / cos, sin of this position) travels with x
   uint32_t pos = 0;
   if constexpr (EPI == EPI_QKV_ROPE) pos = p.state ? p.state->pos : p.pos_imm;
@@ -165,7 +165,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
   }
   if constexpr (EPI == EPI_LOGITS) cta_argmax_partial(p, best_v, best_i, red);
   if constexpr (EPI == EPI_STORE) push_publish(p);
-  kernel_end(p, link_ok);
 }
 
 // Same contract for any K and any alignment (element loads); used when K is not a multiple of the vector width.
@@ -180,7 +179,7 @@ __global__ void __launch_bounds__(kThreads) gemv_scalar_kernel(const GemvParams 
   load_gain(p, xs);
   prefetch_plan(p.pf, kPrefetchChunk);
   pdl_launch_dependents();
-  const bool link_ok = link_wait(p.link);
+  pdl_wait();
   load_x(p, xs, red);
   float best_v = -INFINITY;
   uint32_t best_i = 0xffffffffu;
@@ -198,7 +197,6 @@ __global__ void __launch_bounds__(kThreads) gemv_scalar_kernel(const GemvParams 
   }
   if constexpr (EPI == EPI_LOGITS) cta_argmax_partial(p, best_v, best_i, red);
   if constexpr (EPI == EPI_STORE) push_publish(p);
-  kernel_end(p, link_ok);
 }
 
 template <typename K>
@@ -326,8 +324,10 @@ cudaError_t launch_gemv(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue ep
   if (p.N == 0 || p.K == 0) return cudaErrorInvalidValue;
   if ((epi == EPI_QKV_ROPE || epi == EPI_SILU_MUL) && (p.N % 2) != 0) return cudaErrorInvalidValue;
   int ring_R = 0;
-  if (use_ring(wdtype, epi, p, t, &ring_R))
+  if (use_ring(wdtype, epi, p, t, &ring_R)) {
+    p.l2_ahead = (uint32_t)(t.l2_ahead < 0 ? 0 : t.l2_ahead);
     return launch_gemv_ring(s, wdtype, kvdtype, epi, p, ring_R, t.unroll, t.ctas_per_sm, pdl);
+  }
   const bool vec = vector_ok(wdtype, p);
   const int R = rows_per_warp(epi, vec, t);
   dim3 grid(gemv_grid(wdtype, epi, p, t));

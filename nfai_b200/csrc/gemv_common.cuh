@@ -39,11 +39,32 @@ __device__ __forceinline__ bool pull_wait(const GemvParams& p, uint32_t* s_flag)
   return *s_flag != 0;
 }
 
-__device__ __forceinline__ float pull_value(const GemvParams& p, uint32_t epoch, bool ok, uint32_t i) {
-  DeviceXchgMem mem;
-  const float v = ok ? xchg::sum_slots(mem, p.tp.view, epoch, i, __ldcg(p.tp.pull_resid + i)) : 0.f;
-  if (blockIdx.x == 0 && ok) p.tp.pull_store[i] = v;
-  return v;
+// Four consecutive elements of the pulled x: residual + (sum of the ranks' slots, from zero, in rank order) -- the
+// arithmetic of xchg::sum_slots, with all loads of the batch issued before the first is used (every one is an L2
+// round trip, and up to nine of them feed one element).
+__device__ __forceinline__ float4 pull_value4(const GemvParams& p, uint32_t epoch, bool ok, uint32_t i4) {
+  float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (!ok) return out;
+  const XchgHooks& t = p.tp;
+  const float4* mine = reinterpret_cast<const float4*>(t.view.slots[t.view.rank]);
+  const float4 resid = __ldcg(reinterpret_cast<const float4*>(t.pull_resid) + i4);
+  float4 part[xchg::kMaxWorld];
+#pragma unroll
+  for (int src = 0; src < xchg::kMaxWorld; ++src)
+    part[src] = src < t.view.world ? __ldcg(mine + xchg::slot_offset(epoch, src) / 4 + i4) : out;
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int src = 0; src < xchg::kMaxWorld; ++src) {
+    if (src < t.view.world) {
+      sum.x += part[src].x;
+      sum.y += part[src].y;
+      sum.z += part[src].z;
+      sum.w += part[src].w;
+    }
+  }
+  out = make_float4(resid.x + sum.x, resid.y + sum.y, resid.z + sum.z, resid.w + sum.w);
+  if (blockIdx.x == 0) reinterpret_cast<float4*>(t.pull_store)[i4] = out;
+  return out;
 }
 
 // ss = sum x^2 ; rms = sqrt(ss/K + eps) ; xs = (x / rms) * gain   (RMSNormShader.cs:136-148)
@@ -57,17 +78,53 @@ __device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* re
     pull_ok = pull_wait(p, reinterpret_cast<uint32_t*>(red) + 31);
     pull_epoch = *p.tp.epoch_base + p.tp.pull_index + 1;
   }
-  if (p.gain == nullptr) {
-    for (uint32_t i = tid; i < K; i += kThreads) xs[i] = pull ? pull_value(p, pull_epoch, pull_ok, i) : __ldcg(p.x + i);
+  // x sits in L2 (another kernel, or under tensor parallelism other GPUs, wrote it): the loads of one thread are
+  // issued together, four elements each, before any of them is used.
+  const float* gs = xs + K;  // staged by load_gain() before the dependency wait
+  const bool norm = p.gain != nullptr;
+  float ss = 0.f;
+  if (pull) {  // the host guarantees K % 4 == 0 and 16-byte aligned vectors for a pulling kernel
+    for (uint32_t i = tid; i < (K >> 2); i += kThreads) {
+      const float4 v = pull_value4(p, pull_epoch, pull_ok, i);
+      reinterpret_cast<float4*>(xs)[i] = v;
+      ss = fmaf(v.x, v.x, ss);
+      ss = fmaf(v.y, v.y, ss);
+      ss = fmaf(v.z, v.z, ss);
+      ss = fmaf(v.w, v.w, ss);
+    }
+  } else if ((K & 3u) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
+    const float4* x4 = reinterpret_cast<const float4*>(p.x);
+    const uint32_t n4 = K >> 2;
+    constexpr int B = 4;
+    for (uint32_t base = 0; base < n4; base += B * kThreads) {
+      float4 v[B];
+#pragma unroll
+      for (int j = 0; j < B; ++j) {
+        const uint32_t i = base + j * kThreads + tid;
+        v[j] = i < n4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < B; ++j) {
+        const uint32_t i = base + j * kThreads + tid;
+        if (i < n4) {
+          reinterpret_cast<float4*>(xs)[i] = v[j];
+          ss = fmaf(v[j].x, v[j].x, ss);
+          ss = fmaf(v[j].y, v[j].y, ss);
+          ss = fmaf(v[j].z, v[j].z, ss);
+          ss = fmaf(v[j].w, v[j].w, ss);
+        }
+      }
+    }
+  } else {
+    for (uint32_t i = tid; i < K; i += kThreads) {
+      const float v = p.x[i];
+      xs[i] = v;
+      ss = fmaf(v, v, ss);
+    }
+  }
+  if (!norm) {
     __syncthreads();
     return;
-  }
-  const float* gs = xs + K;  // staged by load_gain() before the dependency wait
-  float ss = 0.f;
-  for (uint32_t i = tid; i < K; i += kThreads) {
-    float v = pull ? pull_value(p, pull_epoch, pull_ok, i) : __ldcg(p.x + i);
-    xs[i] = v;
-    ss = fmaf(v, v, ss);
   }
   ss = warp_sum(ss);
   if ((tid & 31) == 0) red[tid >> 5] = ss;
@@ -78,16 +135,6 @@ __device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* re
   const float rms = sqrtf(__fdiv_rn(tot, (float)K) + p.eps);
   for (uint32_t i = tid; i < K; i += kThreads) xs[i] = __fmul_rn(__fdiv_rn(xs[i], rms), gs[i]);
   __syncthreads();
-}
-
-// Last thing every thread of a GEMV CTA does: report a hand-over that ran out of time, tell the next kernel that this
-// CTA's rows are stored, then the deferred wait for the predecessor's completion (StepLink).
-__device__ __forceinline__ void kernel_end(const GemvParams& p, bool link_ok) {
-  if (!link_ok && threadIdx.x == 0) {
-    if (p.state) atomicOr(&p.state->err, 4u);
-    if (p.err) atomicOr(p.err, 4u);
-  }
-  link_done(p.link);
 }
 
 // ---- tensor-parallel push: the finished row sums of this rank go into its slot on every rank ----------------------

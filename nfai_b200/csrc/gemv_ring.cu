@@ -46,11 +46,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bulk copy global -> this CTA's shared memory; completion is counted in bytes on the mbarrier.
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
+// Bulk copy global -> this CTA's shared memory; completion is counted in bytes on the mbarrier. Weights are read
+// once per token: the lines are marked evict-first in L2 so that they do not push out what other kernels of the
+// step have asked the L2 to hold for them.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
 }
 
 constexpr int kRingSmemHeader = 128;  // bytes: 32 words of reduction scratch
@@ -83,6 +91,7 @@ __global__ void __launch_bounds__(kThreads) gemv_ring_kernel(const GemvParams p)
   const uint32_t my_bar_s = smem_u32(bars + warp * S);
   // whole rows that sit next to each other in memory travel as one copy
   const bool one_copy = nch == 1 && row_bytes == CHUNK;
+  const uint64_t stream_policy = policy_evict_first();
 
   if (lane == 0) {
 #pragma unroll
@@ -102,20 +111,35 @@ __global__ void __launch_bounds__(kThreads) gemv_ring_kernel(const GemvParams p)
     const uint32_t bar = my_bar_s + 8 * s;
     mbar_expect_tx(bar, bytes * rows);
     if (one_copy && rows == (uint32_t)R) {
-      bulk_g2s(my_ring_s + s * kStageBytes, Wb + (size_t)rb * R * row_bytes, kStageBytes, bar);
+      bulk_g2s(my_ring_s + s * kStageBytes, Wb + (size_t)rb * R * row_bytes, kStageBytes, bar, stream_policy);
     } else {
       for (uint32_t r = 0; r < rows; ++r)
-        bulk_g2s(my_ring_s + s * kStageBytes + r * CHUNK, Wb + (size_t)(rb * R + r) * row_bytes + off, bytes, bar);
+        bulk_g2s(my_ring_s + s * kStageBytes + r * CHUNK, Wb + (size_t)(rb * R + r) * row_bytes + off, bytes, bar,
+                 stream_policy);
     }
   };
 
   if (lane == 0) {
     const uint32_t ahead = n_items < (uint32_t)S ? n_items : (uint32_t)S;
     for (uint32_t i = 0; i < ahead; ++i) issue(i, i);  // weights do not depend on the previous kernel
+    // While this kernel waits for its input HBM would idle once the ring is full: ask the L2 for the next stages of
+    // this warp, so that the stream continues and the first refills of the ring are L2 hits.
+    const uint32_t pf_end = n_items < ahead + p.l2_ahead ? n_items : ahead + p.l2_ahead;
+    for (uint32_t i = ahead; i < pf_end; ++i) {
+      const uint32_t rbi = i / nch, c = i - rbi * nch;
+      const uint32_t rb = first + rbi * kWarps;
+      const uint32_t off = c * CHUNK;
+      const uint32_t bytes = row_bytes - off < (uint32_t)CHUNK ? row_bytes - off : (uint32_t)CHUNK;
+      uint32_t rows = p.N - rb * R;
+      rows = rows < (uint32_t)R ? rows : (uint32_t)R;
+      for (uint32_t r = 0; r < rows; ++r)
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(Wb + (size_t)(rb * R + r) * row_bytes + off), "r"(bytes)
+                     : "memory");
+    }
   }
   load_gain(p, xs);
   pdl_launch_dependents();
-  const bool link_ok = link_wait(p.link);
+  pdl_wait();
   uint32_t pos = 0;
   if constexpr (EPI == EPI_QKV_ROPE) pos = p.state ? p.state->pos : p.pos_imm;
   load_x(p, xs, red);
@@ -220,7 +244,6 @@ __global__ void __launch_bounds__(kThreads) gemv_ring_kernel(const GemvParams p)
   }
   if constexpr (EPI == EPI_LOGITS) cta_argmax_partial(p, best_v, best_i, red);
   if constexpr (EPI == EPI_STORE) push_publish(p);
-  kernel_end(p, link_ok);
 }
 
 template <typename Kern>

@@ -9,23 +9,6 @@
 
 namespace nfai {
 
-// How a kernel of the decode step is chained to its neighbours. Without a link a kernel waits for its predecessor
-// to COMPLETE (griddepcontrol.wait), which costs 2-3 microseconds per boundary on top of the work. With a link the
-// kernels, which programmatic dependent launch has made resident together, hand over through a counter in global
-// memory: every CTA of the producer adds one to `done` after its last store (release), every CTA of the consumer
-// polls `wait` until it holds `target` = the producer's CTA count (acquire, bounded), and only then reads the
-// producer's output (with L2 loads). The consumer still executes griddepcontrol.wait, but as its LAST instruction,
-// so kernel completion stays ordered and the wait is off the critical path.
-// No deadlock: the runtime starts a dependent kernel only after every CTA of its predecessor has started, so the
-// predecessor never needs resources the spinning consumer holds; with dependent launch switched off the kernels run
-// one after the other and every counter is already at its target. Counters are zeroed by the first kernel of the step.
-struct StepLink {
-  uint32_t* done = nullptr;        // this kernel's counter (null: nobody polls this kernel)
-  const uint32_t* wait = nullptr;  // the producer's counter (null: wait for the predecessor's completion instead)
-  uint32_t target = 0;
-  unsigned long long wait_ns = 1000000000ull;
-};
-
 // Tensor-parallel hooks of a GEMV launch (world <= 1: none of it is touched). The partial sums of a row-parallel
 // matrix (O and down projections) never go through a separate collective kernel: the GEMV that produces them
 // stores them straight into every rank's exchange area (push) and the GEMV that consumes the sum waits for all
@@ -125,8 +108,8 @@ struct GemvParams {
   PrefetchPlan pf;
   uint32_t* err = nullptr;  // optional device word for error bits when there is no StepState (4 = a bounded wait gave up)
   uint32_t split_log2 = 0;  // filled in by launch_gemv: log2 of the warps that share one row block
+  uint32_t l2_ahead = 0;    // ring modes: stages per warp requested into L2 beyond the ring before the dependency wait
   XchgHooks tp;             // tensor-parallel push / pull (see XchgHooks)
-  StepLink link;            // hand-over from / to the neighbouring kernels of the step (see StepLink)
   // EPI_LOGITS under tensor parallelism: the last CTA reduces the per-CTA partials to this rank's best
   // (value, global index = v_lo + row) and pushes the pair to every rank (exchange tp.push_index)
   uint32_t v_lo = 0;
@@ -140,6 +123,7 @@ struct GemvTune {
   int unroll = 4;         // mode 0: 16-byte loads in flight per row per lane (2, 4 or 8); ring modes: stages per warp (1-4)
   int ctas_per_sm = 2;    // persistent grid = min(needed, 148 * ctas_per_sm) CTAs of 256 threads
   int split = 0;          // mode 0: warps sharing one row block (1, 2, 4, 8); 0 = chosen from the matrix shape
+  int l2_ahead = 0;       // ring modes: stages per warp requested into L2 beyond the ring while the kernel waits
 };
 
 size_t gemv_ring_smem(const GemvParams& p, int chunk_bytes, int S);
@@ -170,7 +154,6 @@ struct AttnParams {
   uint32_t heads_per_cta = 4;  // 4, 2 or 1
   uint32_t min_chunk = 512;
   PrefetchPlan pf;
-  StepLink link;  // hand-over from / to the neighbouring kernels of the step (see StepLink)
 };
 
 
@@ -182,8 +165,6 @@ uint32_t attn_splits(uint32_t qH, uint32_t kvH, uint32_t max_seq, uint32_t heads
                      uint32_t min_chunk = kAttnMinChunk);
 size_t attn_part_floats(uint32_t qH, uint32_t d, uint32_t S_max);
 cudaError_t launch_attn_decode(cudaStream_t s, int kvdtype, const AttnParams& p, bool pdl);
-// CTAs the decode attention launch will have (what a linked consumer waits for).
-uint32_t attn_decode_ctas(const AttnParams& p);
 // Causal attention of T prompt tokens: token t (q row t of p.q, [T][qH*d]) attends to positions 0 .. p.seq_imm-1+t;
 // output rows go to p.out_half ([T][qH*d] float16). One CTA per (KV head group, token), no split.
 cudaError_t launch_attn_prefill(cudaStream_t s, int kvdtype, const AttnParams& p, uint32_t T);
@@ -203,20 +184,17 @@ cudaError_t attn_ring_make_maps(const void* kcache, const void* vcache, uint32_t
                                 AttnTileMaps* out);
 cudaError_t launch_attn_ring(cudaStream_t s, const AttnParams& p, const AttnTileMaps& maps, bool pdl);
 
-// `zero` / `zero_words`: step counters the first kernel of a step clears (see StepLink), or null.
 cudaError_t launch_embed(cudaStream_t s, int wdtype, const void* E, uint32_t H, uint32_t V, StepState* state,
-                         const uint32_t* prompt, uint32_t token_imm, float* x_out, const PrefetchPlan& pf, bool pdl,
-                         uint32_t* zero = nullptr, uint32_t zero_words = 0);
+                         const uint32_t* prompt, uint32_t token_imm, float* x_out, const PrefetchPlan& pf, bool pdl);
 // Reduce the LM head's per-CTA partials to the arg-max (lowest index among maxima), feed it back as the next
 // token and advance the position.
 cudaError_t launch_argmax_final(cudaStream_t s, const float* part_val, const uint32_t* part_idx, uint32_t nparts,
                                 StepState* state, uint32_t* argmax_out, uint32_t* history, uint32_t history_cap,
                                 const PrefetchPlan& pf, uint32_t* xchg_epoch, uint32_t xchg_per_step, const XchgHooks& tp,
-                                bool pdl, const StepLink& link = StepLink());
+                                bool pdl);
 // Head-less prompt step: position and prompt cursor advance by one.
 // xchg_epoch (may be null) counts the tensor-parallel exchanges completed on this context; a step adds its own.
-cudaError_t launch_advance(cudaStream_t s, StepState* state, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl,
-                           const StepLink& link = StepLink());
+cudaError_t launch_advance(cudaStream_t s, StepState* state, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl);
 
 // Temperature / top-k / top-p sampling of `logits` (V floats) on the device. `argmax` points at the index of the
 // largest logit (null: found by an extra kernel). Writes the chosen token to *token_out and, if given, *cur_token;

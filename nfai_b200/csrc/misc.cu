@@ -25,15 +25,8 @@ cudaLaunchConfig_t make_cfg(dim3 grid, dim3 block, cudaStream_t s, cudaLaunchAtt
 template <typename WT>
 __global__ void embed_kernel(const WT* __restrict__ E, uint32_t H, uint32_t V, StepState* state,
                              const uint32_t* __restrict__ prompt, uint32_t token_imm, float* __restrict__ x_out,
-                             const PrefetchPlan pf, uint32_t* zero, uint32_t zero_words) {
+                             const PrefetchPlan pf) {
   prefetch_plan(pf, kPrefetchChunk);
-  // first kernel of a step (plain launch: nothing of the previous step is still running): clear the hand-over
-  // counters of the step before the dependents may start
-  if (zero != nullptr && blockIdx.x == 0) {
-    for (uint32_t i = threadIdx.x; i < zero_words; i += blockDim.x) zero[i] = 0;
-    __threadfence();
-    __syncthreads();
-  }
   pdl_launch_dependents();
   pdl_wait();
   uint32_t tok = token_imm;
@@ -54,13 +47,13 @@ __global__ void __launch_bounds__(256) argmax_final_kernel(const float* __restri
                                                           StepState* state, uint32_t* argmax_out, uint32_t* history,
                                                           uint32_t history_cap, const PrefetchPlan pf,
                                                           uint32_t* xchg_epoch, uint32_t xchg_per_step,
-                                                          const XchgHooks tp, const StepLink link) {
+                                                          const XchgHooks tp) {
   __shared__ float sv[256];
   __shared__ uint32_t si[256];
   __shared__ uint32_t s_ok;
   prefetch_plan(pf, kPrefetchChunk);
   pdl_launch_dependents();
-  if (!link_wait(link) && threadIdx.x == 0 && state) atomicOr(&state->err, 4u);
+  pdl_wait();
   float bv = -INFINITY;
   uint32_t bi = 0xffffffffu;
   if (tp.pull) {
@@ -78,8 +71,8 @@ __global__ void __launch_bounds__(256) argmax_final_kernel(const float* __restri
     if (threadIdx.x == 0 && s_ok) xchg::best_pair(mem, tp.view, epoch, &bv, &bi);
   } else {
     for (uint32_t i = threadIdx.x; i < nparts; i += blockDim.x) {
-      float v = __ldcg(part_val + i);
-      uint32_t ix = __ldcg(part_idx + i);
+      float v = part_val[i];
+      uint32_t ix = part_idx[i];
       if (ix != 0xffffffffu && (bi == 0xffffffffu || v > bv || (v == bv && ix < bi))) {
         bv = v;
         bi = ix;
@@ -114,18 +107,16 @@ __global__ void __launch_bounds__(256) argmax_final_kernel(const float* __restri
       if (xchg_epoch) *xchg_epoch += xchg_per_step;
     }
   }
-  link_done(link);
 }
 
-__global__ void advance_kernel(StepState* state, uint32_t* xchg_epoch, uint32_t xchg_per_step, const StepLink link) {
+__global__ void advance_kernel(StepState* state, uint32_t* xchg_epoch, uint32_t xchg_per_step) {
   pdl_launch_dependents();
-  if (!link_wait(link) && threadIdx.x == 0) atomicOr(&state->err, 4u);
+  pdl_wait();
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     state->pos += 1;
     state->prompt_idx += 1;
     if (xchg_epoch) *xchg_epoch += xchg_per_step;
   }
-  link_done(link);
 }
 
 template <typename ST, typename DT>
@@ -144,33 +135,31 @@ __global__ void ingest_kernel(const IngestParams p) {
 }  // namespace
 
 cudaError_t launch_embed(cudaStream_t s, int wdtype, const void* E, uint32_t H, uint32_t V, StepState* state,
-                         const uint32_t* prompt, uint32_t token_imm, float* x_out, const PrefetchPlan& pf, bool pdl,
-                         uint32_t* zero, uint32_t zero_words) {
+                         const uint32_t* prompt, uint32_t token_imm, float* x_out, const PrefetchPlan& pf, bool pdl) {
   cudaLaunchAttribute attr[1];
   uint32_t blocks = (H + 255) / 256;
   cudaLaunchConfig_t cfg = make_cfg(dim3(blocks), dim3(256), s, attr, pdl);
   if (wdtype == 1)
     return cudaLaunchKernelEx(&cfg, embed_kernel<__half>, reinterpret_cast<const __half*>(E), H, V, state, prompt,
-                              token_imm, x_out, pf, zero, zero_words);
+                              token_imm, x_out, pf);
   return cudaLaunchKernelEx(&cfg, embed_kernel<float>, reinterpret_cast<const float*>(E), H, V, state, prompt,
-                            token_imm, x_out, pf, zero, zero_words);
+                            token_imm, x_out, pf);
 }
 
 cudaError_t launch_argmax_final(cudaStream_t s, const float* part_val, const uint32_t* part_idx, uint32_t nparts,
                                 StepState* state, uint32_t* argmax_out, uint32_t* history, uint32_t history_cap,
                                 const PrefetchPlan& pf, uint32_t* xchg_epoch, uint32_t xchg_per_step, const XchgHooks& tp,
-                                bool pdl, const StepLink& link) {
+                                bool pdl) {
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t cfg = make_cfg(dim3(1), dim3(256), s, attr, pdl);
   return cudaLaunchKernelEx(&cfg, argmax_final_kernel, part_val, part_idx, nparts, state, argmax_out, history,
-                            history_cap, pf, xchg_epoch, xchg_per_step, tp, link);
+                            history_cap, pf, xchg_epoch, xchg_per_step, tp);
 }
 
-cudaError_t launch_advance(cudaStream_t s, StepState* state, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl,
-                           const StepLink& link) {
+cudaError_t launch_advance(cudaStream_t s, StepState* state, uint32_t* xchg_epoch, uint32_t xchg_per_step, bool pdl) {
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t cfg = make_cfg(dim3(1), dim3(32), s, attr, pdl);
-  return cudaLaunchKernelEx(&cfg, advance_kernel, state, xchg_epoch, xchg_per_step, link);
+  return cudaLaunchKernelEx(&cfg, advance_kernel, state, xchg_epoch, xchg_per_step);
 }
 
 cudaError_t launch_ingest(cudaStream_t s, int src_dtype, int dst_dtype, const IngestParams& p) {
