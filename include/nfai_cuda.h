@@ -235,11 +235,13 @@ int nfai_profile_kernel(nfai_model* m, int which, int iters, float* avg_ms, uint
 /* Launch shape of one GEMV kernel of the decode step (selector as in nfai_profile_kernel, 0..4).
  * mode 0: weights double-buffered in registers; rows_per_warp in {1,2,4}, depth = 16-byte loads in flight per row
  *         per lane in {2,4,8}.
- * mode 1 / 2: weights staged through per-warp shared-memory rings by bulk asynchronous copies, stages of
- *         2 rows x 2 KB / 2 rows x 4 KB; rows_per_warp = 2, depth = ring stages per warp in {1,2,3,4}, plus
+ * mode 1: weights staged through per-warp shared-memory rings by bulk asynchronous copies, stages of
+ *         2 rows x 2 KB; rows_per_warp = 2, depth = ring stages per warp in {1,2,3,4}, plus
  *         8 x the number of further stages per warp that are requested into L2 while the kernel waits for its input.
- * The QKV and gate/up kernels need an even rows_per_warp. ctas_per_sm bounds the persistent grid. Results do not
- * depend on the shape. After nfai_model_finalize the decode graphs are captured again.
+ * The QKV and gate/up kernels need an even rows_per_warp. ctas_per_sm bounds the persistent grid (1..16 CTAs per
+ * SM; a value above 16 is taken as the grid's CTA count itself, e.g. 256 so that 8 192 work items make exactly four
+ * rounds over 2 048 warps). rows_per_warp may carry the K split in its upper bits (rows + 16 * split, split in
+ * {1,2,4,8}; 0 = chosen from the matrix shape). Results do not depend on the shape. After nfai_model_finalize the decode graphs are captured again.
 
  * No counterpart in the reference (its dispatch sizes are fixed in each shader class). */
 int nfai_model_tune(nfai_model* m, int which, int mode, int rows_per_warp, int depth, int ctas_per_sm);

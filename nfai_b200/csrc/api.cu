@@ -182,15 +182,16 @@ void read_tune(const char* name, GemvTune& t, int r_default, int u_default) {
   std::string key = std::string("NFAI_TUNE_") + name;
   const char* v = getenv(key.c_str());
   if (v) {
-    int r = 0, u = 0, cps = 0, mode = 0, split = 0, ahead = 0;
-    int got = sscanf(v, "%d,%d,%d,%d,%d,%d", &r, &u, &cps, &mode, &split, &ahead);
+    int r = 0, u = 0, cps = 0, mode = 0, split = 0, ahead = 0, grid = 0;
+    int got = sscanf(v, "%d,%d,%d,%d,%d,%d,%d", &r, &u, &cps, &mode, &split, &ahead, &grid);
     if (got >= 2 && (r == 1 || r == 2 || r == 4) && (u == 1 || u == 2 || u == 3 || u == 4 || u == 8)) {
       t.rows_per_warp = r;
       t.unroll = u;
       if (got >= 3 && cps >= 1 && cps <= 16) t.ctas_per_sm = cps;
-      if (got >= 4 && (mode == 0 || mode == 1 || mode == 2)) t.mode = mode;
+      if (got >= 4 && (mode == 0 || mode == 1)) t.mode = mode;
       if (got >= 5 && (split == 0 || split == 1 || split == 2 || split == 4 || split == 8)) t.split = split;
       if (got >= 6 && ahead >= 0 && ahead <= 64) t.l2_ahead = ahead;
+      if (got >= 7 && grid >= 0 && grid <= 4096) t.grid = grid;
     }
   }
 }
@@ -442,6 +443,7 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     pull_into(gh, 2 * hp.L - 1, x_mid(m, hp.L - 1), x_in(m, hp.L));
     push_from(gh, 2 * hp.L);
     gh.v_lo = m->v_lo;
+    if (fused_x) gh.tp_ticket = tp_ticket_ptr(c->tp);
     STEP(launch_gemv(s, wdt, kvdt, EPI_LOGITS, gh, m->tune_head, pdl_x));
     if (tp_on && !fused_x) {
       e = tp_gather_argmax(c->tp, s, m->part_val, m->part_idx, m->nparts, m->v_lo, &n);
@@ -917,7 +919,7 @@ int nfai_model_finalize(nfai_model* m) {
   const size_t o_h = take((size_t)m->Fl * 4);
   const size_t o_lg = take((size_t)m->Vl * 4);
   // room for every launch shape nfai_model_tune may select later (up to 16 CTAs per SM)
-  const size_t npart_alloc = 148 * 16;
+  const size_t npart_alloc = (size_t)sm_count() * 16;
   m->nparts_alloc = (uint32_t)npart_alloc;
   const size_t o_pv = take(npart_alloc * 4);
   const size_t o_pi = take(npart_alloc * 4);
@@ -944,8 +946,8 @@ int nfai_model_finalize(nfai_model* m) {
   const size_t o_pao = take((size_t)pfc * m->qDimL * 2);
   const size_t o_ph = take((size_t)pfc * m->Fl * 2);
   const size_t o_pt = take((size_t)pfc * 4 + 4);
-  // split-K happens only below 120 output tiles of 128 x 128, with at most 148 CTAs: 148 tiles of partials bound it
-  const size_t pf_part_floats = want_pf && env_int("NFAI_GEMM_SPLIT", 1) ? (size_t)148 * 128 * 128 * 2 : 0;
+  // split-K happens only below 120 output tiles of 128 x 128, with at most one CTA per SM: that many tiles of partials bound it
+  const size_t pf_part_floats = want_pf && env_int("NFAI_GEMM_SPLIT", 1) ? (size_t)sm_count() * 128 * 128 * 2 : 0;
   const size_t o_pp = take(pf_part_floats * 4);
   const size_t o_ss = take(sample_scratch_bytes(m->Vl, nullptr));
   cudaError_t e = cudaMalloc((void**)&m->rarena, off);
@@ -1149,6 +1151,7 @@ static int prefill_batched(nfai_model* m, const uint32_t* tokens, int n) {
     gh.tp.push = 1;
     gh.tp.push_index = 0;
     gh.v_lo = m->v_lo;
+    gh.tp_ticket = tp_ticket_ptr(c->tp);
     CU(c, launch_gemv(s, hp.weight_dtype, kvdt, EPI_LOGITS, gh, m->tune_head, false));
     XchgHooks fin = tp_hooks(c->tp);
     fin.pull = 1;
@@ -1457,7 +1460,13 @@ int nfai_model_tune(nfai_model* m, int which, int mode, int rows_per_warp, int d
               : which == 3 ? &m->tune_o : which == 4 ? &m->tune_head : nullptr;
   if (!t) return fail(c, NFAI_ERR_ARG, "kernel selector must be 0..4");
   const bool even_only = which == 0 || which == 2;
-  bool ok = (mode == 0 || mode == 1 || mode == 2) && ctas_per_sm >= 1 && ctas_per_sm <= 16 && !(even_only && rows_per_warp == 1);
+  // packed knobs: rows_per_warp = rows + 16 * K split (0 = from the shape); ctas_per_sm above 16 = the grid's CTA count
+  const int split = rows_per_warp >> 4;
+  rows_per_warp &= 15;
+  const int grid = ctas_per_sm > 16 ? ctas_per_sm : 0;
+  if (grid) ctas_per_sm = (grid + (int)sm_count() - 1) / (int)sm_count();
+  bool ok = (mode == 0 || mode == 1) && ctas_per_sm >= 1 && ctas_per_sm <= 16 && !(even_only && rows_per_warp == 1) &&
+            (split == 0 || split == 1 || split == 2 || split == 4 || split == 8);
   if (mode == 0)
     ok = ok && (rows_per_warp == 1 || rows_per_warp == 2 || rows_per_warp == 4) && (depth == 2 || depth == 4 || depth == 8) &&
          rows_per_warp * depth <= 16;
@@ -1470,6 +1479,8 @@ int nfai_model_tune(nfai_model* m, int which, int mode, int rows_per_warp, int d
   t->unroll = mode == 0 ? depth : (depth & 7);
   t->l2_ahead = mode == 0 ? 0 : (depth >> 3);
   t->ctas_per_sm = ctas_per_sm;
+  t->grid = grid;
+  t->split = split;
   if (!m->finalized) return NFAI_OK;
   CU(c, cudaSetDevice(c->device));
   CU(c, cudaStreamSynchronize(c->stream));
@@ -1748,7 +1759,7 @@ int nfai_op_lm_head(nfai_ctx* c, const void* W, int dtype, const float* x, const
 }
 
 // Hooks of an op-level call whose exchange areas all sit on this GPU (one per emulated rank). The epoch word
-// (c->dev_err[16]) is zero, so index = epoch - 1; tickets at c->dev_err[18..19].
+// (c->dev_err[16]) is zero, so index = epoch - 1; the LM head's ticket word is c->dev_err[18].
 static int op_xchg_hooks(nfai_ctx* c, void* const* areas, int world, int rank, uint64_t wait_ns, XchgHooks* h) {
   if (!areas || world < 1 || world > xchg::kMaxWorld || rank < 0 || rank >= world) return fail(c, NFAI_ERR_ARG, "bad exchange geometry");
   char* bases[xchg::kMaxWorld] = {};
@@ -1758,7 +1769,6 @@ static int op_xchg_hooks(nfai_ctx* c, void* const* areas, int world, int rank, u
   }
   h->view = xchg::make_view(bases, rank, world);
   h->epoch_base = c->dev_err + 16;
-  h->tickets = c->dev_err + 18;
   h->wait_ns = wait_ns ? wait_ns : c->wait_ns;
   return NFAI_OK;
 }
@@ -1828,6 +1838,7 @@ int nfai_op_lm_head_xchg(nfai_ctx* c, const void* W, int dtype, const float* x, 
     p.tp = h;
     p.tp.push = 1;
     p.tp.push_index = epoch - 1;
+    p.tp_ticket = c->dev_err + 18;
     GemvTune t;
     read_tune("OP", t, 2, 4);
     const uint32_t nparts = gemv_grid(dtype, EPI_LOGITS, p, t);

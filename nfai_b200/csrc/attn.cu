@@ -118,11 +118,11 @@ uint32_t attn_head_groups(uint32_t qH, uint32_t kvH, uint32_t heads_per_cta) {
 }
 
 // Upper bound on the number of splits for a cache of max_seq positions: at least kAttnMinChunk positions per
-// split, and no more CTAs than the 148 SMs hold at once (one 512-thread CTA each), so there is no second wave.
+// split, and no more CTAs than the SMs hold at once (one 512-thread CTA each), so there is no second wave.
 uint32_t attn_splits(uint32_t qH, uint32_t kvH, uint32_t max_seq, uint32_t heads_per_cta, uint32_t min_chunk) {
   uint32_t ctas_x = kvH * attn_head_groups(qH, kvH, heads_per_cta);
   uint32_t by_len = (max_seq + min_chunk - 1) / min_chunk;
-  uint32_t by_sm = 148u / ctas_x;
+  uint32_t by_sm = sm_count() / ctas_x;
   if (by_sm < 1) by_sm = 1;
   uint32_t s = by_len < by_sm ? by_len : by_sm;
   return s < 1 ? 1 : s;

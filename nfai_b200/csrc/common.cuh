@@ -42,23 +42,18 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   return t;
 }
 
-// Memory operations of the tensor-parallel exchange protocol (xchg_protocol.h) on the device: plain stores into
-// peer memory over NVLink, ordered by a system-scope fence before the flag is released; loads of this GPU's own
-// area bypass L1 (another GPU wrote the lines).
+// Memory operations of the tensor-parallel exchange protocol (xchg_protocol.h) on the device: one 8-byte store per
+// word into peer memory over NVLink (delivered whole), volatile 8-byte loads of this GPU's own area (never served
+// from L1: another GPU writes the lines).
 struct DeviceXchgMem {
-  __device__ __forceinline__ void store_f32(float* p, float v) { *p = v; }
-  __device__ __forceinline__ float load_f32(const float* p) { return __ldcg(p); }
-  __device__ __forceinline__ void store_u64(unsigned long long* p, unsigned long long v) { *p = v; }
-  __device__ __forceinline__ unsigned long long load_u64(const unsigned long long* p) { return __ldcg(p); }
-  __device__ __forceinline__ void store_release_u32(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+  __device__ __forceinline__ void store_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
   }
-  __device__ __forceinline__ uint32_t load_acquire_u32(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  __device__ __forceinline__ unsigned long long load_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
   }
-  __device__ __forceinline__ void fence_system() { __threadfence_system(); }
   __device__ __forceinline__ unsigned long long now_ns() { return global_timer_ns(); }
 };
 

@@ -609,7 +609,7 @@ cudaError_t launch_persistent(cudaStream_t s, const __half* A, const __half* W, 
     attr_device = dev;
   }
   const uint32_t tiles = ((M + kBM - 1) / kBM) * ((N + kPBN - 1) / kPBN);
-  return launch_pdl(gemm_tc_persistent_kernel, dim3(tiles < 148 ? tiles : 148), dim3(kGemmThreads), PSmem::kTotal, s,
+  return launch_pdl(gemm_tc_persistent_kernel, dim3(tiles < sm_count() ? tiles : sm_count()), dim3(kGemmThreads), PSmem::kTotal, s,
                     prefill_pdl(), mapA, mapW, M, N, K, ep, err);
 }
 
@@ -621,7 +621,7 @@ uint32_t gemm_tc_splits(uint32_t M, uint32_t N, uint32_t K) {
   const uint32_t tiles = ((M + kBM - 1) / kBM) * ((N + 127) / 128);
   const uint32_t KT = (K + kBK - 1) / kBK;
   if (tiles >= 120) return 1;
-  uint32_t z = 148 / tiles;
+  uint32_t z = sm_count() / tiles;
   if (z > KT / 2) z = KT / 2;
   if (z > 16) z = 16;
   return z < 1 ? 1 : z;

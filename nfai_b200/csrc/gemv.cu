@@ -164,7 +164,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
     }
   }
   if constexpr (EPI == EPI_LOGITS) cta_argmax_partial(p, best_v, best_i, red);
-  if constexpr (EPI == EPI_STORE) push_publish(p);
 }
 
 // Same contract for any K and any alignment (element loads); used when K is not a multiple of the vector width.
@@ -196,7 +195,6 @@ __global__ void __launch_bounds__(kThreads) gemv_scalar_kernel(const GemvParams 
     row_epilogue<KVT, R, EPI>(p, rb * R, acc, best_v, best_i);
   }
   if constexpr (EPI == EPI_LOGITS) cta_argmax_partial(p, best_v, best_i, red);
-  if constexpr (EPI == EPI_STORE) push_publish(p);
 }
 
 template <typename K>
@@ -276,13 +274,9 @@ int rows_per_warp(GemvEpilogue epi, bool vec, const GemvTune& t) {
 
 }  // namespace
 
-static bool use_ring(int wdtype, GemvEpilogue epi, const GemvParams& p, const GemvTune& t, int* chunk) {
-  (void)epi;
-  if ((t.mode != 1 && t.mode != 2) || !vector_ok(wdtype, p)) return false;
-  const int ch = t.mode == 2 ? 4096 : 2048;
-  if (t.unroll < 1 || t.unroll > 4 || gemv_ring_smem(p, ch, t.unroll) > 227 * 1024) return false;
-  *chunk = ch;
-  return true;
+static bool use_ring(int wdtype, const GemvParams& p, const GemvTune& t) {
+  if (t.mode != 1 || !vector_ok(wdtype, p)) return false;
+  return t.unroll >= 1 && t.unroll <= 4 && gemv_ring_smem(p, t.unroll) <= 227 * 1024;
 }
 
 // How many warps share one row block (1, 2, 4 or 8; returned as log2). A matrix with fewer row blocks than the
@@ -298,7 +292,7 @@ static uint32_t gemv_split_log2(int wdtype, bool vec, int R, const GemvParams& p
   const uint32_t U = (uint32_t)t.unroll;
   const uint32_t per_lane = p.K / ve / 32;  // 16-byte vectors per lane per row
   const uint32_t nrb = (p.N + R - 1) / R;
-  const uint32_t warps = kNumSMs * (uint32_t)(t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm) * kWarps;
+  const uint32_t warps = (t.grid > 0 ? (uint32_t)t.grid : sm_count() * (uint32_t)(t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm)) * kWarps;
   if (p.K % (ve * 32) != 0 || per_lane < 4 * U || 2 * nrb > warps) return 0;  // at most half of the warps would work
   for (uint32_t sl = 1; sl <= 3; ++sl) {
     if ((per_lane % (U << sl)) != 0) break;  // chunks must stay whole batches
@@ -308,13 +302,13 @@ static uint32_t gemv_split_log2(int wdtype, bool vec, int R, const GemvParams& p
 }
 
 uint32_t gemv_grid(int wdtype, GemvEpilogue epi, const GemvParams& p, const GemvTune& t) {
-  int ring_R = 0;
-  if (use_ring(wdtype, epi, p, t, &ring_R)) return gemv_ring_grid(p, t.ctas_per_sm);
+  if (use_ring(wdtype, p, t)) return gemv_ring_grid(p, t.ctas_per_sm);
   const bool vec = vector_ok(wdtype, p);
   const int R = rows_per_warp(epi, vec, t);
   const uint32_t nitems = ((p.N + R - 1) / R) << gemv_split_log2(wdtype, vec, R, p, t);
   const uint32_t want = (nitems + kWarps - 1) / kWarps;
-  const uint32_t cap = kNumSMs * (uint32_t)(t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm);  // persistent: warps loop over items
+  uint32_t cap = sm_count() * (uint32_t)(t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm);  // persistent: warps loop over items
+  if (t.grid > 0) cap = (uint32_t)t.grid;
   return want < cap ? want : cap;
 }
 
@@ -323,10 +317,9 @@ cudaError_t launch_gemv(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue ep
   GemvParams p = p_in;
   if (p.N == 0 || p.K == 0) return cudaErrorInvalidValue;
   if ((epi == EPI_QKV_ROPE || epi == EPI_SILU_MUL) && (p.N % 2) != 0) return cudaErrorInvalidValue;
-  int ring_R = 0;
-  if (use_ring(wdtype, epi, p, t, &ring_R)) {
+  if (use_ring(wdtype, p, t)) {
     p.l2_ahead = (uint32_t)(t.l2_ahead < 0 ? 0 : t.l2_ahead);
-    return launch_gemv_ring(s, wdtype, kvdtype, epi, p, ring_R, t.unroll, t.ctas_per_sm, pdl);
+    return launch_gemv_ring(s, wdtype, kvdtype, epi, p, t.unroll, t.ctas_per_sm, pdl);
   }
   const bool vec = vector_ok(wdtype, p);
   const int R = rows_per_warp(epi, vec, t);

@@ -8,89 +8,107 @@ namespace gemv_detail {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr uint32_t kNumSMs = 148;  // B200
 
 // ---- prologue: x (optionally RMS-normalised) into shared memory ----------------------------------------------
 // The gain is a weight: it can be staged in shared memory before the programmatic-dependency wait.
-__device__ __forceinline__ void load_gain(const GemvParams& p, float* xs) {
+__device__ __forceinline__ void load_gain(const GemvParams& p, float* xs, float* gs_at = nullptr) {
   if (p.gain == nullptr) return;
-  float* gs = xs + p.K;
+  float* gs = gs_at ? gs_at : xs + p.K;
   for (uint32_t i = threadIdx.x; i < p.K; i += kThreads) gs[i] = p.gain[i];
 }
 
-// Tensor-parallel input: x = residual + the partial vectors of all ranks, which the previous row-parallel GEMV
-// of every rank pushed into this rank's exchange area. Waits (bounded) for every rank's flag, then adds the slots
-// in rank order, the same order on every rank. CTA 0 keeps the summed vector as the residual stream.
-// When the wait gives up, error bit 4 is raised and x is zero: the kernel still runs to its end.
-__device__ __forceinline__ bool pull_wait(const GemvParams& p, uint32_t* s_flag) {
-  DeviceXchgMem mem;
+// Tensor-parallel input: x = residual + the partial vectors of all ranks, which the previous row-parallel GEMV of
+// every rank stored into this rank's exchange area as (value, epoch) words. Four consecutive elements per call: the
+// words of all ranks are requested together (each is an L2 round trip), re-read (bounded) until every one carries the
+// epoch, then added from zero in rank order -- the arithmetic of xchg::sum_slots, the same on every rank. CTA 0 keeps
+// the summed vector as the residual stream. Returns false when the budget ran out (x is then zero).
+__device__ __forceinline__ bool pull_value4(const GemvParams& p, uint32_t epoch, uint32_t i4, float4* out) {
   const XchgHooks& t = p.tp;
-  const uint32_t epoch = *t.epoch_base + t.pull_index + 1;
-  if (threadIdx.x == 0) *s_flag = 1;
-  __syncthreads();
-  if ((int)threadIdx.x < t.view.world) {
-    if (!xchg::wait_flag(mem, t.view.flags[t.view.rank] + threadIdx.x, epoch, t.wait_ns)) {
-      *s_flag = 0;
-      if (p.state) atomicOr(&p.state->err, 4u);
-      if (p.err) atomicOr(p.err, 4u);
-    }
-  }
-  __syncthreads();
-  return *s_flag != 0;
-}
-
-// Four consecutive elements of the pulled x: residual + (sum of the ranks' slots, from zero, in rank order) -- the
-// arithmetic of xchg::sum_slots, with all loads of the batch issued before the first is used (every one is an L2
-// round trip, and up to nine of them feed one element).
-__device__ __forceinline__ float4 pull_value4(const GemvParams& p, uint32_t epoch, bool ok, uint32_t i4) {
-  float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (!ok) return out;
-  const XchgHooks& t = p.tp;
-  const float4* mine = reinterpret_cast<const float4*>(t.view.slots[t.view.rank]);
+  const uint4* mine = reinterpret_cast<const uint4*>(t.view.slots[t.view.rank]);  // one uint4 = two (value, epoch) words
   const float4 resid = __ldcg(reinterpret_cast<const float4*>(t.pull_resid) + i4);
-  float4 part[xchg::kMaxWorld];
+  uint4 w[xchg::kMaxWorld][2];
+  auto request = [&](int src) {
+    const uint4* q = mine + (xchg::slot_offset(epoch, src) + 4 * (size_t)i4) / 2;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[src][0].x), "=r"(w[src][0].y), "=r"(w[src][0].z), "=r"(w[src][0].w) : "l"(q) : "memory");
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[src][1].x), "=r"(w[src][1].y), "=r"(w[src][1].z), "=r"(w[src][1].w) : "l"(q + 1) : "memory");
+  };
+  auto arrived = [&](int src) {
+    return w[src][0].y == epoch && w[src][0].w == epoch && w[src][1].y == epoch && w[src][1].w == epoch;
+  };
 #pragma unroll
   for (int src = 0; src < xchg::kMaxWorld; ++src)
-    part[src] = src < t.view.world ? __ldcg(mine + xchg::slot_offset(epoch, src) / 4 + i4) : out;
+    if (src < t.view.world) request(src);
+  bool ok = true;
+  unsigned long long t0 = 0;
+  uint32_t polls = 0;
+#pragma unroll
+  for (int src = 0; src < xchg::kMaxWorld; ++src) {
+    if (src < t.view.world) {
+      while (ok && !arrived(src)) {
+        if (t0 == 0) t0 = global_timer_ns();
+        request(src);
+        if ((++polls & 15u) == 0 && global_timer_ns() - t0 > t.wait_ns) ok = false;
+      }
+    }
+  }
   float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
   for (int src = 0; src < xchg::kMaxWorld; ++src) {
     if (src < t.view.world) {
-      sum.x += part[src].x;
-      sum.y += part[src].y;
-      sum.z += part[src].z;
-      sum.w += part[src].w;
+      sum.x += __uint_as_float(w[src][0].x);
+      sum.y += __uint_as_float(w[src][0].z);
+      sum.z += __uint_as_float(w[src][1].x);
+      sum.w += __uint_as_float(w[src][1].z);
     }
   }
-  out = make_float4(resid.x + sum.x, resid.y + sum.y, resid.z + sum.z, resid.w + sum.w);
-  if (blockIdx.x == 0) reinterpret_cast<float4*>(t.pull_store)[i4] = out;
-  return out;
+  *out = ok ? make_float4(resid.x + sum.x, resid.y + sum.y, resid.z + sum.z, resid.w + sum.w) : make_float4(0.f, 0.f, 0.f, 0.f);
+  if (blockIdx.x == 0 && ok) reinterpret_cast<float4*>(t.pull_store)[i4] = *out;
+  return ok;
 }
 
+// Where element k of x sits in shared memory. Natural order for kernels whose lanes read 16 bytes of x per step
+// (float32 weights, and the register streamer). With float16 weights a lane needs 32 bytes per step (elements
+// 8*lane .. 8*lane+7 of a 256-element block); read as two 16-byte loads from the natural order those loads hit every
+// bank twice, and the stream from shared memory is bandwidth-bound on exactly these loads. The permuted order keeps,
+// per 256-element block, the first halves of all lanes together and then the second halves: both loads of a warp
+// cover 512 contiguous bytes.
+template <bool PERM>
+__device__ __forceinline__ uint32_t x_slot4(uint32_t i4) {  // index of the float4 that holds elements 4*i4 .. 4*i4+3
+  if constexpr (!PERM) return i4;
+  const uint32_t r = i4 & 63u;
+  return (i4 & ~63u) + ((r & 1u) << 5) + (r >> 1);
+}
+template <bool PERM>
+__device__ __forceinline__ uint32_t x_slot(uint32_t k) { return 4u * x_slot4<PERM>(k >> 2) + (k & 3u); }
+
 // ss = sum x^2 ; rms = sqrt(ss/K + eps) ; xs = (x / rms) * gain   (RMSNormShader.cs:136-148)
-__device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* red) {
+// With PERM the shared-memory area of x must be a whole number of 256-element blocks.
+template <bool PERM = false>
+__device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* red, const float* gs_in = nullptr) {
   const uint32_t K = p.K;
   const int tid = threadIdx.x;
   const bool pull = p.tp.pull != 0;
-  bool pull_ok = true;
-  uint32_t pull_epoch = 0;
-  if (pull) {
-    pull_ok = pull_wait(p, reinterpret_cast<uint32_t*>(red) + 31);
-    pull_epoch = *p.tp.epoch_base + p.tp.pull_index + 1;
-  }
   // x sits in L2 (another kernel, or under tensor parallelism other GPUs, wrote it): the loads of one thread are
   // issued together, four elements each, before any of them is used.
-  const float* gs = xs + K;  // staged by load_gain() before the dependency wait
+  const float* gs = gs_in ? gs_in : xs + K;  // staged by load_gain() before the dependency wait
   const bool norm = p.gain != nullptr;
   float ss = 0.f;
   if (pull) {  // the host guarantees K % 4 == 0 and 16-byte aligned vectors for a pulling kernel
+    const uint32_t pull_epoch = *p.tp.epoch_base + p.tp.pull_index + 1;
+    bool pull_ok = true;
     for (uint32_t i = tid; i < (K >> 2); i += kThreads) {
-      const float4 v = pull_value4(p, pull_epoch, pull_ok, i);
-      reinterpret_cast<float4*>(xs)[i] = v;
+      float4 v;
+      if (pull_ok) pull_ok = pull_value4(p, pull_epoch, i, &v);
+      else v = make_float4(0.f, 0.f, 0.f, 0.f);
+      reinterpret_cast<float4*>(xs)[x_slot4<PERM>(i)] = v;
       ss = fmaf(v.x, v.x, ss);
       ss = fmaf(v.y, v.y, ss);
       ss = fmaf(v.z, v.z, ss);
       ss = fmaf(v.w, v.w, ss);
+    }
+    if (!pull_ok) {  // a rank did not deliver in time: report, the kernel still runs to its end
+      if (p.state) atomicOr(&p.state->err, 4u);
+      if (p.err) atomicOr(p.err, 4u);
     }
   } else if ((K & 3u) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
     const float4* x4 = reinterpret_cast<const float4*>(p.x);
@@ -107,7 +125,7 @@ __device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* re
       for (int j = 0; j < B; ++j) {
         const uint32_t i = base + j * kThreads + tid;
         if (i < n4) {
-          reinterpret_cast<float4*>(xs)[i] = v[j];
+          reinterpret_cast<float4*>(xs)[x_slot4<PERM>(i)] = v[j];
           ss = fmaf(v[j].x, v[j].x, ss);
           ss = fmaf(v[j].y, v[j].y, ss);
           ss = fmaf(v[j].z, v[j].z, ss);
@@ -118,7 +136,7 @@ __device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* re
   } else {
     for (uint32_t i = tid; i < K; i += kThreads) {
       const float v = p.x[i];
-      xs[i] = v;
+      xs[x_slot<PERM>(i)] = v;
       ss = fmaf(v, v, ss);
     }
   }
@@ -133,35 +151,36 @@ __device__ __forceinline__ void load_x(const GemvParams& p, float* xs, float* re
 #pragma unroll
   for (int w = 0; w < kWarps; ++w) tot += red[w];
   const float rms = sqrtf(__fdiv_rn(tot, (float)K) + p.eps);
-  for (uint32_t i = tid; i < K; i += kThreads) xs[i] = __fmul_rn(__fdiv_rn(xs[i], rms), gs[i]);
+  for (uint32_t i = tid; i < K; i += kThreads) {
+    const uint32_t j = x_slot<PERM>(i);
+    xs[j] = __fmul_rn(__fdiv_rn(xs[j], rms), gs[i]);
+  }
   __syncthreads();
 }
 
 // ---- tensor-parallel push: the finished row sums of this rank go into its slot on every rank ----------------------
+// Each value travels with the exchange's epoch in one 8-byte word; two neighbouring rows go out as one 16-byte store
+// (two independent words: a reader checks the epoch of each). Nothing else is needed to publish them.
 template <int R>
 __device__ __forceinline__ void push_rows(const GemvParams& p, uint32_t row0, const float (&acc)[R]) {
-  DeviceXchgMem mem;
+  const xchg::View& v = p.tp.view;
   const uint32_t epoch = *p.tp.epoch_base + p.tp.push_index + 1;
+  const size_t base = xchg::slot_offset(epoch, v.rank);
 #pragma unroll
-  for (int r = 0; r < R; ++r)
-    if (row0 + r < p.N) xchg::push_value(mem, p.tp.view, epoch, row0 + r, acc[r]);
-}
-
-// Every thread of every CTA of a pushing kernel calls this once, after its last row: the CTAs draw tickets and
-// the last one tells every rank that this rank's vector is complete. The barrier orders the CTA's peer stores
-// before thread 0's system-scope fence; the ticket (device scope) makes the last CTA's fence cover all of them.
-__device__ __forceinline__ void push_publish(const GemvParams& p) {
-  if (!p.tp.push) return;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    DeviceXchgMem mem;
-    uint32_t* ticket = p.tp.tickets + (p.tp.push_index & 1u);
-    __threadfence_system();
-    const uint32_t t = atomicAdd(ticket, 1u);
-    if (t == gridDim.x - 1) {
-      *ticket = 0;  // the next pushing kernel that uses this word starts after this one has ended
-      __threadfence_system();
-      xchg::publish(mem, p.tp.view, *p.tp.epoch_base + p.tp.push_index + 1);
+  for (int r = 0; r < R; r += 2) {
+    const uint32_t n = row0 + r;
+    if (n >= p.N) break;
+    if (r + 1 < R && n + 1 < p.N && (n & 1u) == 0) {
+      for (int dst = 0; dst < v.world; ++dst) {
+        unsigned long long* q = v.slots[dst] + base + n;
+        asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(q), "r"(__float_as_uint(acc[r])), "r"(epoch),
+                     "r"(__float_as_uint(acc[r + 1])), "r"(epoch)
+                     : "memory");
+      }
+    } else {
+      DeviceXchgMem mem;
+      xchg::push_value(mem, v, epoch, n, acc[r]);
+      if (r + 1 < R && n + 1 < p.N) xchg::push_value(mem, v, epoch, n + 1, acc[r + 1]);
     }
   }
 }
@@ -358,7 +377,7 @@ __device__ __forceinline__ void cta_argmax_partial(const GemvParams& p, float be
   }
   if (!p.tp.push) return;
   uint32_t* s_last = redi + 30;
-  uint32_t* ticket = p.tp.tickets + (p.tp.push_index & 1u);
+  uint32_t* ticket = p.tp_ticket;
   if (threadIdx.x == 0) {
     __threadfence();
     *s_last = atomicAdd(ticket, 1u) == gridDim.x - 1 ? 1u : 0u;

@@ -11,13 +11,13 @@ namespace nfai {
 
 // Tensor-parallel hooks of a GEMV launch (world <= 1: none of it is touched). The partial sums of a row-parallel
 // matrix (O and down projections) never go through a separate collective kernel: the GEMV that produces them
-// stores them straight into every rank's exchange area (push) and the GEMV that consumes the sum waits for all
-// ranks' flags and adds the slots in rank order while it loads x (pull). Protocol: xchg_protocol.h.
+// stores them, each value tagged with the exchange's epoch, straight into every rank's exchange area (push), and the
+// GEMV that consumes the sum polls its own area for the tagged words and adds them in rank order while it loads x
+// (pull). Protocol: xchg_protocol.h.
 struct XchgHooks {
   xchg::View view{};                     // every rank's exchange area (own entry = local memory)
   const uint32_t* epoch_base = nullptr;  // device word: exchanges completed on this context before this step
-  uint32_t* tickets = nullptr;           // two local words: CTAs of a pushing kernel draw tickets, the last publishes
-  unsigned long long wait_ns = 1000000000ull;  // budget of the flag wait; afterwards error bit 4 and a zero x
+  unsigned long long wait_ns = 1000000000ull;  // budget of the wait for a word; afterwards error bit 4 and a zero x
   int pull = 0;                          // x = pull_resid + sum over ranks of exchange pull_index of this step
   uint32_t pull_index = 0;
   const float* pull_resid = nullptr;
@@ -33,6 +33,9 @@ template <typename Kern>
 inline cudaError_t prefer_max_shared(Kern kernel) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
 }
+
+// Streaming multiprocessors of the current device (148 on a B200); persistent grids are sized from it.
+uint32_t sm_count();
 
 // Launch with programmatic stream serialisation: the kernel may be scheduled while its predecessor in the stream is
 // still running; it must execute griddepcontrol.wait (pdl_wait) before it touches anything the predecessor wrote.
@@ -110,26 +113,30 @@ struct GemvParams {
   uint32_t split_log2 = 0;  // filled in by launch_gemv: log2 of the warps that share one row block
   uint32_t l2_ahead = 0;    // ring modes: stages per warp requested into L2 beyond the ring before the dependency wait
   XchgHooks tp;             // tensor-parallel push / pull (see XchgHooks)
-  // EPI_LOGITS under tensor parallelism: the last CTA reduces the per-CTA partials to this rank's best
-  // (value, global index = v_lo + row) and pushes the pair to every rank (exchange tp.push_index)
+  // EPI_LOGITS under tensor parallelism: the CTA that finishes last (ticket in `tp_ticket`, a local word) reduces
+  // the per-CTA partials to this rank's best (value, global index = v_lo + row) and pushes the pair to every rank
+  // (exchange tp.push_index)
   uint32_t v_lo = 0;
+  uint32_t* tp_ticket = nullptr;
 };
 
 // Tunable launch shape of the GEMV family.
 struct GemvTune {
-  int mode = 0;           // 0 = register double-buffered streamer, 1 / 2 = shared-memory rings fed by bulk copies,
-                          // stages of 2 rows x 2 KB / 2 rows x 4 KB
+  int mode = 0;           // 0 = register double-buffered streamer, 1 = per-warp shared-memory rings fed by bulk copies
+                          // (stages of 2 rows x 2 KB)
   int rows_per_warp = 2;  // mode 0: 1, 2 or 4 (EPI_QKV_ROPE and EPI_SILU_MUL need an even value); ring modes: always 2
   int unroll = 4;         // mode 0: 16-byte loads in flight per row per lane (2, 4 or 8); ring modes: stages per warp (1-4)
   int ctas_per_sm = 2;    // persistent grid = min(needed, 148 * ctas_per_sm) CTAs of 256 threads
   int split = 0;          // mode 0: warps sharing one row block (1, 2, 4, 8); 0 = chosen from the matrix shape
   int l2_ahead = 0;       // ring modes: stages per warp requested into L2 beyond the ring while the kernel waits
+  int grid = 0;           // 0 = 148 * ctas_per_sm; else the CTA count (chosen so that the work items divide evenly
+                          // over the grid's warps and no last round runs partly empty)
 };
 
-size_t gemv_ring_smem(const GemvParams& p, int chunk_bytes, int S);
+size_t gemv_ring_smem(const GemvParams& p, int S);
 uint32_t gemv_ring_grid(const GemvParams& p, int ctas_per_sm);
-cudaError_t launch_gemv_ring(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue epi, const GemvParams& p,
-                             int chunk_bytes, int S, int ctas_per_sm, bool pdl);
+cudaError_t launch_gemv_ring(cudaStream_t s, int wdtype, int kvdtype, GemvEpilogue epi, const GemvParams& p, int S,
+                             int ctas_per_sm, bool pdl);
 
 // Number of CTAs the launch will use (the LM head needs it to size its partial buffers).
 uint32_t gemv_grid(int wdtype, GemvEpilogue epi, const GemvParams& p, const GemvTune& t);

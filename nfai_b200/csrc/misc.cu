@@ -5,6 +5,19 @@
 
 namespace nfai {
 
+uint32_t sm_count() {
+  // per device: contexts on different GPUs may live in one process
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return (uint32_t)cached[dev];
+}
+
 namespace {
 
 cudaLaunchConfig_t make_cfg(dim3 grid, dim3 block, cudaStream_t s, cudaLaunchAttribute* attr, bool pdl) {
@@ -58,17 +71,19 @@ __global__ void __launch_bounds__(256) argmax_final_kernel(const float* __restri
   uint32_t bi = 0xffffffffu;
   if (tp.pull) {
     // tensor parallel: every rank's LM-head kernel pushed its best (value, global index) into this rank's area
-    DeviceXchgMem mem;
-    const uint32_t epoch = *tp.epoch_base + tp.pull_index + 1;
-    if (threadIdx.x == 0) s_ok = 1;
-    __syncthreads();
-    if ((int)threadIdx.x < tp.view.world &&
-        !xchg::wait_flag(mem, tp.view.pair_flags[tp.view.rank] + threadIdx.x, epoch, tp.wait_ns)) {
-      s_ok = 0;
-      if (state) atomicOr(&state->err, 4u);
+    if (threadIdx.x == 0) {
+      DeviceXchgMem mem;
+      const uint32_t epoch = *tp.epoch_base + tp.pull_index + 1;
+      float v = 0.f;
+      uint32_t ix = 0xffffffffu;
+      s_ok = xchg::best_pair(mem, tp.view, epoch, tp.wait_ns, &v, &ix) ? 1u : 0u;
+      if (s_ok) {
+        bv = v;
+        bi = ix;
+      } else if (state) {
+        atomicOr(&state->err, 4u);
+      }
     }
-    __syncthreads();
-    if (threadIdx.x == 0 && s_ok) xchg::best_pair(mem, tp.view, epoch, &bv, &bi);
   } else {
     for (uint32_t i = threadIdx.x; i < nparts; i += blockDim.x) {
       float v = part_val[i];
@@ -165,7 +180,8 @@ cudaError_t launch_advance(cudaStream_t s, StepState* state, uint32_t* xchg_epoc
 cudaError_t launch_ingest(cudaStream_t s, int src_dtype, int dst_dtype, const IngestParams& p) {
   if (p.n == 0) return cudaSuccess;
   uint64_t want = (p.n + 255) / 256;
-  dim3 grid((unsigned)(want < 148ull * 16 ? want : 148ull * 16)), block(256);
+  const uint64_t cap = (uint64_t)sm_count() * 16;
+  dim3 grid((unsigned)(want < cap ? want : cap)), block(256);
   if (src_dtype == 0 && dst_dtype == 0) ingest_kernel<float, float><<<grid, block, 0, s>>>(p);
   else if (src_dtype == 0 && dst_dtype == 1) ingest_kernel<float, __half><<<grid, block, 0, s>>>(p);
   else if (src_dtype == 1 && dst_dtype == 0) ingest_kernel<__half, float><<<grid, block, 0, s>>>(p);

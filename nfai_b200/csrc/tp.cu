@@ -215,10 +215,11 @@ XchgHooks tp_hooks(TpComm* tp) {
   XchgHooks h;
   h.view = tp->view;
   h.epoch_base = tp_epoch_ptr(tp);
-  h.tickets = tp_epoch_ptr(tp) + 2;
   h.wait_ns = tp->wait_ns;
   return h;
 }
+
+uint32_t* tp_ticket_ptr(TpComm* tp) { return tp_epoch_ptr(tp) + 2; }
 
 void tp_set_wait_ns(TpComm* tp, unsigned long long ns) { tp->wait_ns = ns ? ns : 1; }
 

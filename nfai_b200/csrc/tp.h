@@ -31,9 +31,11 @@ cudaError_t tp_allreduce_residual(TpComm* tp, cudaStream_t s, float* buf, const 
 cudaError_t tp_allreduce(TpComm* tp, cudaStream_t s, float* buf, size_t n);
 
 // After tp_import_peer_descs: the exchanges run inside the GEMV kernels (push in the epilogue of the producer, pull
-// in the prologue of the consumer; xchg_protocol.h). tp_hooks gives the view, epoch word, tickets and wait budget.
+// in the prologue of the consumer; xchg_protocol.h). tp_hooks gives the view, epoch word and wait budget.
 bool tp_push_ready(const TpComm* tp);
 XchgHooks tp_hooks(TpComm* tp);
+// Local word for the "last CTA reduces" ticket of the vocabulary-sharded LM head.
+uint32_t* tp_ticket_ptr(TpComm* tp);
 void tp_set_wait_ns(TpComm* tp, unsigned long long ns);
 
 // Peer-memory exchange buffers. Every rank exports a 128-byte descriptor of its buffer (process id, device

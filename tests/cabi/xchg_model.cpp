@@ -5,8 +5,9 @@
 //   xchg_model <world> <exchanges> <H> [stall_rank stall_at]
 //
 // Every rank runs `exchanges` rounds shaped like a one-layer decode step: two vector exchanges back to back (push a
-// partial vector, publish, wait for all ranks (bounded), sum in rank order with a residual), then the arg-max pair
-// exchange. Ranks are delayed at random so that they drift as far apart
+// partial vector as (value, epoch) words, poll the own area until every word carries the epoch (bounded), sum in rank
+// order with a residual), then the arg-max pair exchange. The only synchronisation is the 8-byte word itself
+// (relaxed atomics here, single 8-byte stores on the device). Ranks are delayed at random so that they drift as far apart
 // as the protocol allows. Checked: every rank computes bit-identical sums, equal to the sum taken in rank order on
 // one thread; the pair exchange picks the lowest index among equal maxima; epochs survive the 2^32 wrap.
 // With stall_rank/stall_at, that rank stops before publishing exchange stall_at: the others must give up after
@@ -26,17 +27,8 @@
 using namespace nfai::xchg;
 
 struct HostMem {
-  void store_f32(float* p, float v) { __atomic_store(p, &v, __ATOMIC_RELAXED); }
-  float load_f32(const float* p) {
-    float v;
-    __atomic_load(const_cast<float*>(p), &v, __ATOMIC_RELAXED);
-    return v;
-  }
   void store_u64(unsigned long long* p, unsigned long long v) { __atomic_store_n(p, v, __ATOMIC_RELAXED); }
   unsigned long long load_u64(const unsigned long long* p) { return __atomic_load_n(p, __ATOMIC_RELAXED); }
-  void store_release_u32(uint32_t* p, uint32_t v) { __atomic_store_n(p, v, __ATOMIC_RELEASE); }
-  uint32_t load_acquire_u32(const uint32_t* p) { return __atomic_load_n(p, __ATOMIC_ACQUIRE); }
-  void fence_system() { __atomic_thread_fence(__ATOMIC_SEQ_CST); }
   unsigned long long now_ns() {
     return (unsigned long long)std::chrono::duration_cast<std::chrono::nanoseconds>(
                std::chrono::steady_clock::now().time_since_epoch())
@@ -60,18 +52,14 @@ int main(int argc, char** argv) {
   if (world < 1 || world > kMaxWorld || H == 0 || H > kMaxH) return 2;
   const unsigned long long budget_ns = stall_rank >= 0 ? 20ull * 1000 * 1000 : 5ull * 1000 * 1000 * 1000;
   // epochs start just below the 32-bit wrap so that the comparison is exercised across it
-  const uint32_t epoch0 = 0xffffffffu - rounds;  // three epochs per round: the wrap falls a third of the way in
+  // three epochs per round: the count passes the 32-bit wrap a third of the way in (epoch 0 then names an exchange
+  // whose slots have long been written, so it cannot be mistaken for fresh memory)
+  const uint32_t epoch0 = 0xffffffffu - rounds;
 
   std::vector<std::vector<char>> areas(world, std::vector<char>(kAreaBytes));
   std::vector<char*> base(world);
   for (int r = 0; r < world; ++r) {
     base[r] = areas[r].data();
-    // flag words start at the epoch before the first exchange, as a context that has run epoch0 exchanges would
-    View v = make_view(base.data(), r, 1);
-    (void)v;
-    uint32_t* f = reinterpret_cast<uint32_t*>(base[r] + kFlagsOffset);
-    uint32_t* pf = reinterpret_cast<uint32_t*>(base[r] + kPairFlagsOffset);
-    for (int s = 0; s < kMaxWorld; ++s) f[s] = pf[s] = epoch0;
   }
   std::vector<std::vector<float>> results(world, std::vector<float>((size_t)2 * rounds * H, 0.f));
   std::vector<std::vector<uint32_t>> winners(world, std::vector<uint32_t>(rounds, 0));
@@ -88,27 +76,24 @@ int main(int argc, char** argv) {
         const uint32_t epoch = epoch0 + 3 * e + 1 + half;  // consecutive epochs: the two parities alternate
         if (rng() % 4 == 0) std::this_thread::sleep_for(std::chrono::microseconds(rng() % 200));
         for (uint32_t i = 0; i < H; ++i) push_value(mem, v, epoch, i, partial_of(rank, 2 * e + half, i));
-        mem.fence_system();
-        publish(mem, v, epoch);
-        for (int src = 0; src < world; ++src)
-          if (!wait_flag(mem, v.flags[rank] + src, epoch, budget_ns)) {
+        for (uint32_t i = 0; i < H; ++i) {
+          float x;
+          if (!sum_slots(mem, v, epoch, i, 0.25f * i, budget_ns, &x)) {
             timed_out[rank] = 1;
             return;
           }
-        for (uint32_t i = 0; i < H; ++i)
-          results[rank][((size_t)2 * e + half) * H + i] = sum_slots(mem, v, epoch, i, 0.25f * i);
+          results[rank][((size_t)2 * e + half) * H + i] = x;
+        }
       }
       // pair exchange: ranks r and r^1 tie on the value, the lower global index must win
       const uint32_t pe = epoch0 + 3 * e + 3;
       push_pair(mem, v, pe, (float)((e + rank / 2) % 7), 1000u * (uint32_t)rank + e % 5);
-      for (int src = 0; src < world; ++src)
-        if (!wait_flag(mem, v.pair_flags[rank] + src, pe, budget_ns)) {
-          timed_out[rank] = 1;
-          return;
-        }
       float bv;
       uint32_t bi;
-      best_pair(mem, v, pe, &bv, &bi);
+      if (!best_pair(mem, v, pe, budget_ns, &bv, &bi)) {
+        timed_out[rank] = 1;
+        return;
+      }
       winners[rank][e] = bi;
       completed[rank] = e + 1;
     }

@@ -54,12 +54,14 @@ def test_gemv(cuda_ctx, oracle, N, K, dtype, norm, resid):
 
 
 @pytest.mark.parametrize("shape", ["1,2,2,0", "1,8,2,0", "2,2,1,0", "2,8,4,0", "4,2,2,0", "4,4,2,0",
-                                   "1,2,1,1", "1,4,2,1", "1,6,1,1", "2,2,1,1", "2,3,1,1", "2,4,2,1"])
+                                   "2,1,2,1", "2,2,2,1", "2,2,1,1", "2,3,1,1", "2,4,1,1", "2,3,1,1,0,5"])
 @pytest.mark.parametrize("N,K,dtype", [(203, 1544, np.float16), (64, 256, np.float32), (1000, 2048, np.float16),
                                        (37, 8192, np.float16), (5000, 520, np.float32)])
 def test_gemv_launch_shapes(cuda_ctx, oracle, monkeypatch, shape, N, K, dtype):
-    """Every tunable launch shape (rows per warp, depth, CTAs per SM, mode 0 = registers / 1 = shared-memory
-    ring fed by bulk copies) computes the same thing, through every epilogue."""
+    """Every tunable launch shape (rows per warp, depth, CTAs per SM, mode 0 = registers / 1 = shared-memory rings fed by
+    bulk copies with `depth` stages per warp, K split, stages asked into L2 ahead) computes the same thing, through
+    every epilogue. K = 2 048 with float16 weights takes the ring kernel's x-in-registers form, the other shapes its
+    shared-memory form (ragged chunks, float32 weights)."""
     monkeypatch.setenv("NFAI_TUNE_OP", shape)
     rng = np.random.default_rng(N + K)
     W = (rng.standard_normal((N, K)) * 0.05).astype(dtype)
