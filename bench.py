@@ -380,7 +380,8 @@ def run_ours(args, cfg):
         "clocks": clocks,
         "load_s": load_s, "prefill_tok_s": PROMPT_LEN / prefill_s,
         "prefill": {"tokens": PROMPT_LEN, "ms": prefill_s * 1e3, "tok_s": PROMPT_LEN / prefill_s,
-                    "path": "batched tensor-core GEMM" if (cfg.dtype == "f16" and world == 1) else "token by token",
+                    "path": ("batched tensor-core GEMM" + (", NCCL all-reduce of [tokens][H] after O and down" if world > 1 else ""))
+                            if cfg.dtype == "f16" else "token by token",
                     "tflops": (2.0 * (cfg.streamed_matrix_params() - cfg.V * cfg.H) * PROMPT_LEN
                                + 2.0 * PROMPT_LEN * PROMPT_LEN * cfg.qDim * cfg.L) / prefill_s / 1e12},
     }
@@ -417,11 +418,14 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill-2048", action="store_true", help="skip the 2 048-token prompt measurement")
+    ap.add_argument("--min-timed-s", type=float, default=1.0,
+                    help="repeat the K-step loop until this much device time is measured (0: one repetition, for profilers)")
     ap.add_argument("--nccl-allreduce", action="store_true", help="N > 1: use NCCL all-reduces instead of the peer-memory kernel")
     ap.add_argument("--prompt-len", type=int, default=0,
                     help="0 = the configuration's own prompt length (c1 128, c2 2048, c3 1024, c4 32768)")
     args = ap.parse_args()
-    global PROMPT_LEN
+    global PROMPT_LEN, MIN_TIMED_S
+    MIN_TIMED_S = args.min_timed_s
     PROMPT_LEN = args.prompt_len or {"c2": 2048, "c3": 1024, "c4": 32768}.get(args.config, 128)
     from nfai_b200 import synth
     cfg = synth.get_config(args.config)

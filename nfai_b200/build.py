@@ -93,9 +93,24 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+def build_step_model() -> str:
+    """The stand-alone model of the decode step (csrc/step_model.cu): a diagnostic program, not part of the library."""
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    exe = os.path.join(OBJ_DIR, "step_model")
+    cmd = [_nvcc(), *_host_compiler_flags(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+           os.path.join(CSRC, "step_model.cu"), "-o", exe]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for step_model.cu:\n{r.stdout}\n{r.stderr}")
+    return exe
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--step-model", action="store_true", help="also build the decode-step timing model (build/step_model)")
     a = ap.parse_args()
     print(build(a.force, a.verbose))
+    if a.step_model:
+        print(build_step_model())

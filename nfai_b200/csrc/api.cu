@@ -235,6 +235,7 @@ AttnParams attn_params(nfai_model* m, uint32_t l) {
   a.S_max = m->S_max;
   a.heads_per_cta = m->attn_heads;
   a.min_chunk = kAttnMinChunk;
+  a.early = env_int("NFAI_ATTN_EARLY", 1) != 0;
   return a;
 }
 

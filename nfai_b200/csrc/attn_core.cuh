@@ -207,7 +207,9 @@ __device__ __forceinline__ void attn_core(const AttnParams& p, const uint32_t bx
   if (s >= S_eff) return;
   const uint32_t t0 = s * chunk;
   const uint32_t t1 = min(seq, t0 + chunk);
-  const uint32_t newest = seq - 1;  // the row the producing kernel of this step writes
+  // the row the producing kernel of this step writes; with p.early == 0 the wait comes first and no row is special
+  if (!p.early) pdl_wait();
+  const uint32_t newest = p.early ? seq - 1 : 0xffffffffu;
 
   const KVT* kc = reinterpret_cast<const KVT*>(p.kcache) + g * D + sub * 8;
   const KVT* vc = reinterpret_cast<const KVT*>(p.vcache) + g * D + sub * 8;
@@ -224,7 +226,7 @@ __device__ __forceinline__ void attn_core(const AttnParams& p, const uint32_t bx
     kr[u] = early ? KV8<KVT>::template ld<CG>(kc + (size_t)t * kvDim) : KV8<KVT>::zero();
     vr[u] = early ? KV8<KVT>::template ld<CG>(vc + (size_t)t * kvDim) : KV8<KVT>::zero();
   }
-  pdl_wait();
+  if (p.early) pdl_wait();
 #pragma unroll
   for (int u = 0; u < UNR; ++u) {
     const uint32_t t = base + u * (kAW * PPW) + grp;

@@ -160,6 +160,7 @@ struct AttnParams {
   // context in flight at once) and the fewest positions a CTA takes before the range is split.
   uint32_t heads_per_cta = 4;  // 4, 2 or 1
   uint32_t min_chunk = 512;
+  uint32_t early = 1;  // request the K/V rows of earlier positions before the dependency wait (0: wait first)
   PrefetchPlan pf;
 };
 

@@ -138,7 +138,9 @@ class TensorSource:
         self.cfg, self.seed = cfg, seed
         self.specs = list(tensor_specs(cfg))
         self.index = {name: i for i, (name, _ne, _dt) in enumerate(self.specs)}
-        self.workers = workers or max(1, min(8, (os.cpu_count() or 2) - 1))
+        # one process per GPU shares the host cores: divide them among the ranks
+        ranks = max(1, int(os.environ.get("LOCAL_WORLD_SIZE", os.environ.get("WORLD_SIZE", "1")) or 1))
+        self.workers = workers or max(1, min(8, ((os.cpu_count() or 2) - 1) // ranks))
         self.pool = cf.ThreadPoolExecutor(max_workers=self.workers)
         self.futures = {}
 
