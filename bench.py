@@ -35,8 +35,10 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel (FFN gate/up GEMV of configs[1]
 # on one GPU), from an ncu capture of this kernel; it goes stale when the kernel's memory behaviour changes, so the
 # capture it came from is named beside it.
-NCU_TRAFFIC = {("c1", 1): {"bytes": 67155200 + 453376,
-                           "capture": "ncu --set full, one launch of the gate/up GEMV inside a decode step"}}
+NCU_TRAFFIC = {("c1", 1): {"bytes": 67165440 + 270848,
+                           "capture": "ncu --set full --clock-control none -k regex:gemv_kernel -s 170 -c 4 of "
+                                      "bench.py --steps 2 --warmup 3 --prompt-len 2 --min-timed-s 0: the gate/up launch "
+                                      "(67.165 MB read + 0.271 MB written against 67.117 MB algorithmic)"}}
 PROMPT_LEN = 128
 MIN_TIMED_S = 1.0  # the K-step loop is repeated until this much device time has been measured; the median is reported
 
@@ -228,7 +230,10 @@ def run_ours(args, cfg):
             _tp.connect_peers(dist, factory.ctx, device="cuda")
             exchange = "peer-memory push all-reduce (own kernel over NVLink)"
     t_load = time.perf_counter()
-    model = LlamaModel(factory.ctx, synth.metadata(cfg), synthetic_tensors(cfg, args.seed), ctx_size,
+    # the ranks of a tensor-parallel job share the generation of the synthetic weights (each tensor is made by one
+    # rank and broadcast), so that the host cores do it once
+    shared = dict(dist=dist, device=torch.device("cuda", local_rank)) if dist is not None else {}
+    model = LlamaModel(factory.ctx, synth.metadata(cfg), synthetic_tensors(cfg, args.seed, **shared), ctx_size,
                        kv_dtype=args.kv_dtype)
     load_s = time.perf_counter() - t_load
     prompt = synth.prompt_ids(cfg, PROMPT_LEN, args.seed)

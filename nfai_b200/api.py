@@ -330,10 +330,11 @@ class LlamaModelFactory:
         self.ctx.close()
 
 
-def synthetic_tensors(cfg, seed: int = 0) -> List[ComputeCollection]:
-    """The seeded synthetic model as lazy in-memory ComputeCollections (no file)."""
+def synthetic_tensors(cfg, seed: int = 0, dist=None, device=None) -> List[ComputeCollection]:
+    """The seeded synthetic model as lazy in-memory ComputeCollections (no file). With `dist` (an initialised
+    torch.distributed module) and `device` the ranks of the job share the work of generating it."""
     from . import synth
-    src = synth.TensorSource(cfg, seed)
+    src = synth.SharedTensorSource(cfg, seed, dist, device) if dist is not None else synth.TensorSource(cfg, seed)
     return [_LazySynth(src, name, ne, dt) for name, ne, dt in src.specs]
 
 

@@ -21,7 +21,7 @@ LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libnfai_cuda.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
-SOURCES = ["api.cu", "gemv.cu", "gemv_ring.cu", "gemm_tc.cu", "attn.cu", "attn_ring.cu", "attn_prefill_tc.cu", "attn_static.cu", "misc.cu", "tp.cu", "gguf_loader.cu", "sample.cu", "tokenizer.cpp"]
+SOURCES = ["api.cu", "gemv.cu", "gemv_ring.cu", "gemm_tc.cu", "attn.cu", "attn_ring.cu", "attn_mma.cu", "attn_prefill_tc.cu", "attn_static.cu", "misc.cu", "tp.cu", "gguf_loader.cu", "sample.cu", "tokenizer.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -132,6 +132,7 @@ struct nfai_model {
   uint32_t S_max = 1;
   uint32_t attn_heads = 4;  // query heads per attention CTA in the decode step
   std::vector<AttnTileMaps> attn_maps;  // per layer, when the decode step uses the tile-staged attention kernel
+  bool attn_mma = false;                // long float16 caches: the tensor-core attention kernel (default over the tile-staged one)
   StepState* state = nullptr;
   uint32_t* history = nullptr;
   uint32_t* prompt = nullptr;
@@ -413,7 +414,8 @@ cudaError_t record_step(nfai_model* m, bool with_head, bool from_prompt, int* la
     STEP(launch_gemv(s, wdt, kvdt, EPI_QKV_ROPE, gq, m->tune_qkv, l > 0 ? pdl_x : pdl));
     AttnParams ga = attn_params(m, l);
     ga.pf = pp.next(end_of(LW.qkv), false);
-    if (!m->attn_maps.empty()) STEP(launch_attn_ring(s, ga, m->attn_maps[l], pdl));
+    if (m->attn_mma) STEP(launch_attn_mma(s, ga, pdl));
+    else if (!m->attn_maps.empty()) STEP(launch_attn_ring(s, ga, m->attn_maps[l], pdl));
     else STEP(launch_attn_decode(s, kvdt, ga, pdl));
     GemvParams go = o_params(m, l);
     go.pf = pp.next(end_of(LW.o), true);
@@ -957,7 +959,9 @@ int nfai_model_finalize(nfai_model* m) {
   m->kc = m->rarena + o_kc; m->vc = m->rarena + o_vc;
   // long float16 caches: attention through tile-staged rings (NFAI_ATTN_RING=0 keeps the register streamer, 1 forces it)
   m->attn_maps.clear();
-  if (m->attn_heads == 4 && attn_ring_supported(hp.kv_dtype, hp.d) && ring_wanted(hp.ctx)) {
+  // long float16 caches: attention on the tensor cores (NFAI_ATTN_MMA=0: the tile-staged CUDA-core kernel instead)
+  m->attn_mma = m->attn_heads == 4 && attn_mma_supported(hp.kv_dtype, hp.d) && ring_wanted(hp.ctx) && env_int("NFAI_ATTN_MMA", 1) != 0;
+  if (!m->attn_mma && m->attn_heads == 4 && attn_ring_supported(hp.kv_dtype, hp.d) && ring_wanted(hp.ctx)) {
     m->attn_maps.resize(hp.L);
     for (uint32_t l = 0; l < hp.L; ++l) {
       const size_t lo = (size_t)l * kv_layer_elems(m) * kvs;
@@ -1570,6 +1574,7 @@ int nfai_profile_kernel(nfai_model* m, int which, int iters, float* avg_ms, uint
       case 3: return launch_gemv(c->stream, wdt, kvdt, EPI_STORE, o_params(m, l), m->tune_o, false);
       case 4: return launch_gemv(c->stream, wdt, kvdt, EPI_LOGITS, head_params(m), m->tune_head, false);
       default:
+        if (m->attn_mma) return launch_attn_mma(c->stream, attn_params(m, l), false);
         if (!m->attn_maps.empty()) return launch_attn_ring(c->stream, attn_params(m, l), m->attn_maps[l], false);
         return launch_attn_decode(c->stream, kvdt, attn_params(m, l), false);
     }
@@ -1706,6 +1711,8 @@ int nfai_op_attn_decode(nfai_ctx* c, const float* q, const void* kcache, const v
   size_t tick_off = align_up(attn_part_floats(qH, d, a.S_max) * 4, 256);
   a.tickets = (uint32_t*)((char*)scratch + tick_off);
   CU(c, cudaMemsetAsync(a.tickets, 0, (size_t)kvH * attn_head_groups(qH, kvH) * 4, c->stream));
+  if (attn_mma_supported(kv_dtype, d) && ring_wanted(seq) && env_int("NFAI_ATTN_MMA", 1) != 0)
+    return op_end(c, launch_attn_mma(c->stream, a, false));
   if (attn_ring_supported(kv_dtype, d) && ring_wanted(seq)) {
     AttnTileMaps maps;
     if (attn_ring_make_maps(kcache, vcache, seq, kvH * d, d, &maps) == cudaSuccess) return op_end(c, launch_attn_ring(c->stream, a, maps, false));

@@ -192,6 +192,11 @@ cudaError_t attn_ring_make_maps(const void* kcache, const void* vcache, uint32_t
                                 AttnTileMaps* out);
 cudaError_t launch_attn_ring(cudaStream_t s, const AttnParams& p, const AttnTileMaps& maps, bool pdl);
 
+// Long-context variant on the tensor cores (float16 cache, d = 64 or 128, up to four query heads per CTA as the rows
+// of a 16-row MMA tile): same grid, scratch and merge as the kernels above.
+bool attn_mma_supported(int kvdtype, uint32_t d);
+cudaError_t launch_attn_mma(cudaStream_t s, const AttnParams& p, bool pdl);
+
 cudaError_t launch_embed(cudaStream_t s, int wdtype, const void* E, uint32_t H, uint32_t V, StepState* state,
                          const uint32_t* prompt, uint32_t token_imm, float* x_out, const PrefetchPlan& pf, bool pdl);
 // Reduce the LM head's per-CTA partials to the arg-max (lowest index among maxima), feed it back as the next

@@ -378,6 +378,7 @@ __global__ void __launch_bounds__(256) consume_rate(const uint4* fill, float* y,
     for (int v = 0; v < 8; ++v)
       for (int e = 0; e < 8; ++e) xr[v][e] = xs[v * 256 + lane * 8 + e];
   float total = 0.f;
+  asm volatile("" ::: "memory");
   const long long t0 = clock64();
   for (int it = 0; it < rep; ++it) {
     float acc[kR] = {0.f, 0.f};
@@ -405,8 +406,9 @@ __global__ void __launch_bounds__(256) consume_rate(const uint4* fill, float* y,
       }
     }
     total += acc[0] + acc[1];
-    asm volatile("" ::: "memory");  // the next repetition reads shared memory again
+    asm volatile("" : "+f"(total) : : "memory");  // the next repetition reads shared memory again
   }
+  asm volatile("" : "+f"(total) : : "memory");    // the sums exist before the clock is read
   const long long t1 = clock64();
   total = warp_sum(total);
   if (lane == 0) y[blockIdx.x * 8 + warp] = total;

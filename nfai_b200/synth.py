@@ -161,6 +161,43 @@ class TensorSource:
         self.futures.clear()
 
 
+class SharedTensorSource(TensorSource):
+    """The same tensors for several ranks of one job without every rank generating all of them: tensor i is generated
+    by rank i mod world and broadcast over the job's process group (device to device), so the host cores generate the
+    model once instead of once per rank. Every rank must ask for the tensors in the same order."""
+
+    def __init__(self, cfg: ModelConfig, seed: int, dist, device):
+        import os
+        self.dist, self.device = dist, device
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        cpus = (os.cpu_count() or 2) - 1
+        super().__init__(cfg, seed, workers=max(1, min(8, cpus // max(1, int(os.environ.get("LOCAL_WORLD_SIZE", self.world))))))
+
+    def _submit(self, i: int):
+        if i % self.world == self.rank:
+            super()._submit(i)
+
+    def get(self, name: str) -> np.ndarray:
+        import torch
+        i = self.index[name]
+        _n, ne, dt = self.specs[i]
+        owner = i % self.world
+        np_dtype = np.float16 if (dt == "f16" and not name.endswith("_norm.weight")) else np.float32
+        shape = tuple(reversed(ne))
+        if owner == self.rank:
+            for j in range(i, i + self.world * (self.workers + 1), self.world):
+                self._submit(j)
+            arr = np.ascontiguousarray(self.futures.pop(i).result())
+            assert arr.dtype == np_dtype and arr.shape == shape, (name, arr.dtype, arr.shape)
+            t = torch.from_numpy(arr.reshape(-1).view(np.uint8)).to(self.device)
+        else:
+            t = torch.empty(int(np.prod(shape)) * np.dtype(np_dtype).itemsize, dtype=torch.uint8, device=self.device)
+        self.dist.broadcast(t, src=owner)
+        if owner != self.rank:
+            arr = t.cpu().numpy().view(np_dtype).reshape(shape)
+        return arr
+
+
 def iter_tensors(cfg: ModelConfig, seed: int = 0) -> Iterator[Tuple[str, Tuple[int, ...], str, np.ndarray]]:
     src = TensorSource(cfg, seed)
     try:

@@ -232,9 +232,12 @@ def test_argmax_ties_pick_the_lowest_index(cuda_ctx, oracle):
 
 
 @pytest.mark.parametrize("qH,kvH,d", [(32, 8, 64), (24, 8, 128), (4, 2, 64), (8, 1, 64), (6, 2, 128)])
-@pytest.mark.parametrize("seq", [1, 2, 15, 16, 17, 100, 700, 5000, 20000, 32768])
-def test_attention_tile_staged_kernel_every_length(cuda_ctx, oracle, monkeypatch, qH, kvH, d, seq):
-    """The long-context kernel (K and V through shared-memory rings) forced on for every length of a float16 cache."""
+@pytest.mark.parametrize("seq", [1, 2, 15, 16, 17, 100, 255, 256, 257, 700, 5000, 20000, 32768])
+@pytest.mark.parametrize("kernel", ["tensor-core", "tile-staged"])
+def test_attention_long_context_kernels_every_length(cuda_ctx, oracle, monkeypatch, qH, kvH, d, seq, kernel):
+    """The two long-context kernels (query heads as the rows of an MMA tile; K and V through shared-memory rings on the
+    CUDA cores) forced on for every length of a float16 cache."""
+    monkeypatch.setenv("NFAI_ATTN_MMA", "1" if kernel == "tensor-core" else "0")
     if seq == 20000 and (qH, kvH, d) not in ((32, 8, 64), (24, 8, 128)):
         pytest.skip("the longest sequences on few geometries only")
     if seq == 32768 and (qH, kvH, d) != (32, 8, 64):

@@ -94,3 +94,33 @@ def test_shard_ranges_cover_every_matrix_once():
             assert cover.all() or cols.all()
     with pytest.raises(ValueError):
         tp.shard_ranges(synth.get_config("c0"), 4, 0)  # kvH = 2 does not divide by 4
+
+
+def _shared_source_worker(rank: int, world: int, port: int):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+
+    from nfai_b200 import synth
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        cfg = synth.get_config("s3", gain_std=0.1)
+        src = synth.SharedTensorSource(cfg, 0, dist, torch.device("cpu"))
+        same = True
+        for name, ne, dt in src.specs:
+            a = src.get(name)
+            b = synth.gen_tensor(cfg, name, ne, dt, 0)
+            same = same and a.dtype == b.dtype and a.shape == b.shape and bool(np.array_equal(a, b))
+        src.close()
+        return same
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ranks_share_the_generation_of_the_synthetic_model():
+    """Every tensor is generated by one rank and broadcast: all ranks end up with exactly the tensors a single process
+    generates (the benchmark uses this so that N ranks do not generate the model N times)."""
+    from .mp_util import run_ranks
+    assert run_ranks(_shared_source_worker, 2, timeout=120, port_base=29300) == [True, True]
