@@ -125,6 +125,7 @@ uint32_t attn_splits(uint32_t qH, uint32_t kvH, uint32_t max_seq, uint32_t heads
   uint32_t by_sm = sm_count() / ctas_x;
   if (by_sm < 1) by_sm = 1;
   uint32_t s = by_len < by_sm ? by_len : by_sm;
+  if (s > (uint32_t)attn_detail::kAttnMergeCap) s = attn_detail::kAttnMergeCap;  // the merge keeps one weight per split in shared memory
   return s < 1 ? 1 : s;
 }
 
@@ -136,7 +137,7 @@ cudaError_t launch_attn_prefill(cudaStream_t s, int kvdtype, const AttnParams& p
 }
 
 cudaError_t launch_attn_decode(cudaStream_t s, int kvdtype, const AttnParams& p, bool pdl) {
-  if (p.qH == 0 || p.kvH == 0 || p.qH % p.kvH != 0 || p.S_max == 0) return cudaErrorInvalidValue;
+  if (p.qH == 0 || p.kvH == 0 || p.qH % p.kvH != 0 || p.S_max == 0 || p.S_max > (uint32_t)attn_detail::kAttnMergeCap) return cudaErrorInvalidValue;
   if (!p.state && p.seq_imm == 0) return cudaErrorInvalidValue;
   if (p.heads_per_cta != 1 && p.heads_per_cta != 2 && p.heads_per_cta != 4) return cudaErrorInvalidValue;
   return kvdtype == 1 ? launch_d<__half>(s, p, pdl) : launch_d<float>(s, p, pdl);

@@ -61,6 +61,61 @@ struct KV8<__half> {
   }
 };
 
+// Last step of a split sequence, run by the CTA that drew the last ticket of its (KV head, head group): the partials
+// (unnormalised sums, m, l) of the S_eff splits of heads h0 .. h0 + nh - 1 are merged and the output is written.
+// A warp per head turns the m's into weights (lanes along the splits: one round trip to L2 for any S_eff <= 32), then
+// every thread adds one output element over the splits with eight loads in flight -- a loop of dependent loads here
+// costs a round trip per split, microseconds at 18 splits. Every thread of the CTA calls it (one block barrier).
+constexpr int kAttnMergeCap = 256;  // upper bound on S_max (attn_splits never returns more)
+template <int D, int NT>
+__device__ __forceinline__ void attn_merge_splits(const AttnParams& p, const uint32_t h0, const uint32_t nh, const uint32_t S_eff) {
+  constexpr int STR = D + 2;
+  __shared__ float mw[4][kAttnMergeCap];
+  __shared__ float mlinv[4];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (uint32_t j = warp; j < nh; j += NT / 32) {
+    const float* bp = p.part + (size_t)(h0 + j) * p.S_max * STR;
+    float mk[kAttnMergeCap / 32];
+    float M = kNegBig;
+#pragma unroll
+    for (int u = 0; u < kAttnMergeCap / 32; ++u) {
+      const uint32_t k = lane + 32 * u;
+      mk[u] = k < S_eff ? __ldcg(bp + k * STR + D) : kNegBig;
+      M = fmaxf(M, mk[u]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float ls = 0.f;
+#pragma unroll
+    for (int u = 0; u < kAttnMergeCap / 32; ++u) {
+      const uint32_t k = lane + 32 * u;
+      if (k < S_eff) {
+        const float w = __expf(mk[u] - M);
+        mw[j][k] = w;
+        ls = fmaf(__ldcg(bp + k * STR + D + 1), w, ls);
+      }
+    }
+    ls = warp_sum(ls);
+    if (lane == 0) mlinv[j] = 1.0f / ls;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < (int)nh * D; idx += NT) {
+    const int j = idx / D, i = idx % D;
+    const float* bp = p.part + (size_t)(h0 + j) * p.S_max * STR + i;
+    float O = 0.f;
+    uint32_t k = 0;
+    for (; k + 8 <= S_eff; k += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcg(bp + (size_t)(k + u) * STR);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) O = fmaf(v[u], mw[j][k + u], O);
+    }
+    for (; k < S_eff; ++k) O = fmaf(__ldcg(bp + (size_t)k * STR), mw[j][k], O);
+    p.out[(h0 + j) * D + i] = O * mlinv[j];
+  }
+}
+
 // Second half of the attention of one CTA: every lane holds an online-softmax state (m, l, acc) over its own
 // positions for up to kG query heads; merge lanes -> warps -> (if the sequence was split) CTAs, and write the output.
 // Every thread of the CTA must call it (block barriers).
@@ -158,19 +213,7 @@ __device__ __forceinline__ void attn_finish(const AttnParams& p, const uint32_t 
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  for (int idx = tid; idx < (int)nh * D; idx += kAT) {
-    const int j = idx / D, i = idx % D;
-    const float* bp = p.part + (size_t)(h0 + j) * p.S_max * pstride;
-    float M = kNegBig;
-    for (uint32_t k = 0; k < S_eff; ++k) M = fmaxf(M, __ldcg(bp + k * pstride + D));
-    float Lsum = 0.f, O = 0.f;
-    for (uint32_t k = 0; k < S_eff; ++k) {
-      const float w = __expf(__ldcg(bp + k * pstride + D) - M);
-      Lsum = fmaf(__ldcg(bp + k * pstride + D + 1), w, Lsum);
-      O = fmaf(__ldcg(bp + k * pstride + i), w, O);
-    }
-    p.out[(h0 + j) * D + i] = O * (1.0f / Lsum);
-  }
+  attn_merge_splits<D, kAT>(p, h0, nh, S_eff);
   if (tid == 0) p.tickets[bx] = 0;  // ready for the next launch
 }
 

@@ -284,19 +284,7 @@ __global__ void __launch_bounds__(kMThreads, 1) attn_mma_kernel(const AttnParams
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  for (int idx = tid; idx < (int)nh * D; idx += kMThreads) {
-    const int j = idx / D, i = idx % D;
-    const float* bp = p.part + (size_t)(h0 + j) * p.S_max * STR;
-    float M = kNegBig;
-    for (uint32_t k = 0; k < S_eff; ++k) M = fmaxf(M, __ldcg(bp + k * STR + D));
-    float Lsum = 0.f, O = 0.f;
-    for (uint32_t k = 0; k < S_eff; ++k) {
-      const float w = __expf(__ldcg(bp + k * STR + D) - M);
-      Lsum = fmaf(__ldcg(bp + k * STR + D + 1), w, Lsum);
-      O = fmaf(__ldcg(bp + k * STR + i), w, O);
-    }
-    p.out[(h0 + j) * D + i] = O * (1.0f / Lsum);
-  }
+  attn_detail::attn_merge_splits<D, kMThreads>(p, h0, nh, S_eff);
   if (tid == 0) p.tickets[bx] = 0;  // ready for the next launch
 }
 
@@ -315,7 +303,7 @@ cudaError_t launch_mma_d(cudaStream_t s, const AttnParams& p, bool pdl) {
 bool attn_mma_supported(int kvdtype, uint32_t d) { return kvdtype == 1 && (d == 64 || d == 128); }
 
 cudaError_t launch_attn_mma(cudaStream_t s, const AttnParams& p, bool pdl) {
-  if (p.qH == 0 || p.kvH == 0 || p.qH % p.kvH != 0 || p.S_max == 0 || p.out_half) return cudaErrorInvalidValue;
+  if (p.qH == 0 || p.kvH == 0 || p.qH % p.kvH != 0 || p.S_max == 0 || p.S_max > (uint32_t)attn_detail::kAttnMergeCap || p.out_half) return cudaErrorInvalidValue;
   if (!p.state && p.seq_imm == 0) return cudaErrorInvalidValue;
   if (((uintptr_t)p.kcache | (uintptr_t)p.vcache) & 15) return cudaErrorInvalidValue;
   switch (p.d) {

@@ -326,7 +326,7 @@ cudaError_t attn_ring_make_maps(const void* kcache, const void* vcache, uint32_t
 }
 
 cudaError_t launch_attn_ring(cudaStream_t s, const AttnParams& p, const AttnTileMaps& maps, bool pdl) {
-  if (p.qH == 0 || p.kvH == 0 || p.qH % p.kvH != 0 || p.S_max == 0 || p.out_half) return cudaErrorInvalidValue;
+  if (p.qH == 0 || p.kvH == 0 || p.qH % p.kvH != 0 || p.S_max == 0 || p.S_max > (uint32_t)attn_detail::kAttnMergeCap || p.out_half) return cudaErrorInvalidValue;
   if (!p.state && p.seq_imm == 0) return cudaErrorInvalidValue;
   const bool two = ring_stages() == 2;
   switch (p.d) {

@@ -386,7 +386,9 @@ __global__ void __launch_bounds__(256) consume_rate(const uint4* fill, float* y,
       const unsigned char* st = my + (size_t)s * kR * kChunk;
 #pragma unroll
       for (int v = 0; v < kChunk / 512; ++v) {
-        const uint32_t vb = (lane + 32 * v) * 16;
+        // the same bytes every repetition, rotated by 16 bytes per repetition (same bank pattern): the address depends
+        // on the repetition, so no load can be kept from one repetition to the next
+        const uint32_t vb = ((lane + 32 * v + it) * 16) & (kChunk - 1);
         float4 x0, x1;
         if (MODE == 0) {
           const float4* xp = reinterpret_cast<const float4*>(xs + ((s & 1) * kChunk + vb) / 2);
@@ -426,16 +428,29 @@ void run_consume(const char* tag) {
   CK(cudaMemset(fill, 0x11, 4096 * 16));
   CK(cudaMalloc(&y, 148 * 8 * 4));
   CK(cudaMalloc(&cyc, 148 * 8));
-  const int rep = 50;
-  for (int i = 0; i < 2; ++i) consume_rate<MODE><<<148, 256, smem>>>(fill, y, cyc, rep);
+  const int rep = 2000;
+  cudaEvent_t e0, e1;
+  CK(cudaEventCreate(&e0));
+  CK(cudaEventCreate(&e1));
+  consume_rate<MODE><<<148, 256, smem>>>(fill, y, cyc, rep);
+  CK(cudaGetLastError());
+  CK(cudaEventRecord(e0));
+  consume_rate<MODE><<<148, 256, smem>>>(fill, y, cyc, rep);
+  CK(cudaEventRecord(e1));
+  CK(cudaGetLastError());
   CK(cudaDeviceSynchronize());
+  float ms = 0.f;
+  CK(cudaEventElapsedTime(&ms, e0, e1));
   std::vector<unsigned long long> h(148);
   CK(cudaMemcpy(h.data(), cyc, 148 * 8, cudaMemcpyDeviceToHost));
   double avg = 0;
   for (auto c : h) avg += (double)c;
   avg /= 148;
   const double bytes = 8.0 * 3 * kR * kChunk * rep;
-  printf("consume from shared memory, %-32s: %.1f bytes of weights per clock per SM (HBM delivers ~23)\n", tag, bytes / avg);
+  printf("consume from shared memory, %-36s: %.1f bytes of weights per clock per SM (%.0f GB/s per SM by the event clock; HBM delivers ~23 B/clk)\n",
+         tag, bytes / avg, bytes / (ms * 1e-3) * 1e-9);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
   cudaFree(fill);
   cudaFree(y);
   cudaFree(cyc);
