@@ -82,8 +82,10 @@ __global__ void __launch_bounds__(kMThreads, 1) attn_mma_kernel(const AttnParams
   constexpr int STR = D + 2;              // one partial in scratch: D accumulators, m, l
   constexpr int SSTR = D + 4;
   extern __shared__ __align__(16) unsigned char mma_smem[];
-  __shared__ __align__(16) float wpart[kMW][kMG][SSTR];  // per-warp partials (unnormalised o, m, l)
-  __shared__ float fin_scale[kMW][kMG];
+  constexpr int kRowsMax = 64;                                // rows of partials merged per pass
+  constexpr int kRegion = ((kRowsMax + 2) * STR + 4 + 3) / 4 * 4;  // floats per head in the merge buffer
+  static_assert(kRowsMax >= kMW, "the warps' rows are the first pass");
+  __shared__ float fin_scale[kRowsMax + 1][kMG];
   __shared__ float fin_ML[kMG][2];
   __shared__ uint32_t is_last;
 
@@ -237,61 +239,127 @@ __global__ void __launch_bounds__(kMThreads, 1) attn_mma_kernel(const AttnParams
   }
   cp_async_wait_all_but<0>();
 
-  // ---- this warp's partial of the real rows, natural-log domain for the merge
+  // ---- merge. One routine adds rows of (unnormalised sums, m, l): first the rows of the eight warps, then -- in the
+  // CTA that drew the last ticket of its (KV head, head group) -- the rows of all splits, copied from scratch into the
+  // shared memory the stages occupied (L2-only 16-byte copies, all in flight at once). The routine is one piece of
+  // code run by every CTA, so the last CTA finds it in the instruction caches; what only the last CTA runs (the copy
+  // loop) is a few instructions. (Code run once per launch is fetched from HBM behind 67 MB of K and V: a merge that
+  // unrolled its loads per split cost more in instruction fetch than it saved in round trips.)
+  // Rows of head j lie STR floats apart from mrow0 + j * kRegion + (misalignment of the scratch rows, 0 or 2 floats);
+  // two more rows per head carry the running result when the splits do not fit one pass.
+  __syncthreads();  // every warp is past its last read of its stages
+  float* const mbuf = reinterpret_cast<float*>(mma_smem);
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
-  if ((uint32_t)qr < nh) {
+  if ((uint32_t)qr < nh) {  // natural-log domain for the merge
+    float* row = mbuf + qr * kRegion + warp * STR;
 #pragma unroll
-    for (int j = 0; j < D / 8; ++j) *reinterpret_cast<float2*>(&wpart[warp][qr][j * 8 + qc]) = make_float2(o[j][0], o[j][1]);
+    for (int j = 0; j < D / 8; ++j) *reinterpret_cast<float2*>(row + j * 8 + qc) = make_float2(o[j][0], o[j][1]);
     if ((lane & 3) == 0) {
-      wpart[warp][qr][D] = m_a * 0.6931471805599453f;
-      wpart[warp][qr][D + 1] = l_a;
+      row[D] = m_a * 0.6931471805599453f;
+      row[D + 1] = l_a;
     }
   }
-  __syncthreads();
-  // ---- merge the warps of the CTA (a warp that saw no position holds m = kNegBig, l = 0: weight exp(-inf) = 0)
-  if (tid < kMG) {
-    float M = kNegBig;
-    for (int w = 0; w < kMW; ++w) M = fmaxf(M, wpart[w][tid][D]);
-    float Lsum = 0.f;
-    for (int w = 0; w < kMW; ++w) {
-      const float scw = __expf(wpart[w][tid][D] - M);
-      fin_scale[w][tid] = scw;
-      Lsum = fmaf(wpart[w][tid][D + 1], scw, Lsum);
-    }
-    fin_ML[tid][0] = M;
-    fin_ML[tid][1] = Lsum;
-  }
-  __syncthreads();
-  for (int idx = tid; idx < (int)nh * D; idx += kMThreads) {
-    const int j = idx / D, i = idx % D;
-    float acc = 0.f;
+  uint32_t cnt = kMW, k0 = 0, k_next = 0, carry_rd = 0;
+  bool global_phase = false, has_carry = false;
+#pragma unroll 1
+  for (;;) {
+    __syncthreads();  // the rows of this pass are in place
+    const uint32_t n = cnt + (has_carry ? 1u : 0u);
+    auto rowp = [&](uint32_t j, uint32_t r) -> const float* {
+      const float* base = mbuf + j * kRegion;
+      if (r >= cnt) return base + 4 + (kRowsMax + carry_rd) * STR;
+      const uint32_t mis = global_phase ? (uint32_t)((((size_t)(h0 + j) * p.S_max + k0) * STR) & 3) : 0u;
+      return base + mis + r * STR;
+    };
+    // (a warp, or a split, that saw no position holds m = kNegBig, l = 0: weight exp(-inf) = 0)
+    if (warp < (int)nh) {  // warp j turns the m's of head j into weights, lanes along the rows
+      static_assert(kRowsMax + 1 <= 96, "three rows per lane");
+      float mr[3], M = kNegBig;
 #pragma unroll
-    for (int w = 0; w < kMW; ++w) acc = fmaf(wpart[w][j][i], fin_scale[w][j], acc);
-    if (S_eff == 1) p.out[(h0 + j) * D + i] = acc * (1.0f / fin_ML[j][1]);
-    else p.part[((size_t)(h0 + j) * p.S_max + s) * STR + i] = acc;
+      for (int u = 0; u < 3; ++u) {
+        const uint32_t r = lane + 32 * u;
+        mr[u] = r < n ? rowp(warp, r)[D] : kNegBig;
+        M = fmaxf(M, mr[u]);
+      }
+#pragma unroll
+      for (int o2 = 16; o2 > 0; o2 >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o2));
+      float Lsum = 0.f;
+#pragma unroll
+      for (int u = 0; u < 3; ++u) {
+        const uint32_t r = lane + 32 * u;
+        if (r < n) {
+          const float scw = __expf(mr[u] - M);
+          fin_scale[r][warp] = scw;
+          Lsum = fmaf(rowp(warp, r)[D + 1], scw, Lsum);
+        }
+      }
+      Lsum = warp_sum(Lsum);
+      if (lane == 0) {
+        fin_ML[warp][0] = M;
+        fin_ML[warp][1] = Lsum;
+      }
+    }
+    __syncthreads();
+    const bool final_pass = global_phase ? k_next >= S_eff : S_eff == 1;
+    const uint32_t carry_wr = has_carry ? carry_rd ^ 1u : 0u;
+    for (int idx = tid; idx < (int)nh * D; idx += kMThreads) {
+      const int j = idx / D, i = idx % D;
+      float acc = 0.f;
+#pragma unroll 4
+      for (uint32_t r = 0; r < n; ++r) acc = fmaf(rowp(j, r)[i], fin_scale[r][j], acc);
+      if (final_pass) p.out[(h0 + j) * D + i] = acc * (1.0f / fin_ML[j][1]);
+      else if (!global_phase) p.part[((size_t)(h0 + j) * p.S_max + s) * STR + i] = acc;
+      else mbuf[j * kRegion + 4 + (kRowsMax + carry_wr) * STR + i] = acc;
+    }
+    if (final_pass) break;
+    if (!global_phase) {
+      // several splits: publish the partial, the last CTA of this (kv head, head group) goes on
+      if (tid < (int)nh) {
+        float* pp = p.part + ((size_t)(h0 + tid) * p.S_max + s) * STR;
+        pp[D] = fin_ML[tid][0];
+        pp[D + 1] = fin_ML[tid][1];
+      }
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) is_last = atomicAdd(&p.tickets[bx], 1u) == S_eff - 1 ? 1u : 0u;
+      __syncthreads();
+      if (!is_last) return;
+      __threadfence();
+      global_phase = true;
+    } else {
+      if (tid < (int)nh) {
+        float* cr = mbuf + tid * kRegion + 4 + (kRowsMax + carry_wr) * STR;
+        cr[D] = fin_ML[tid][0];
+        cr[D + 1] = fin_ML[tid][1];
+      }
+      carry_rd = carry_wr;
+      has_carry = true;
+      __syncthreads();  // every thread is past its reads of this pass's rows
+    }
+    // the next rows of every head: whole 16-byte pieces around them (scratch rows are 8-byte aligned)
+    k0 = k_next;
+    cnt = min(S_eff - k_next, (uint32_t)kRowsMax);
+    k_next += cnt;
+    for (uint32_t j = 0; j < nh; ++j) {
+      const size_t first = ((size_t)(h0 + j) * p.S_max + k0) * STR;
+      const uint32_t mis = (uint32_t)(first & 3);
+      const uint32_t pieces = (mis + cnt * STR + 3) / 4;
+      const float* src = p.part + (first - mis);
+      float* dst = mbuf + j * kRegion;
+      for (uint32_t c = tid; c < pieces; c += kMThreads) cp_async16((uint32_t)__cvta_generic_to_shared(dst + 4 * c), src + 4 * c, 16u);
+    }
+    cp_async_commit();
+    cp_async_wait_all_but<0>();
   }
-  if (S_eff == 1) return;
-  // ---- several splits: publish the partial, the last CTA of this (kv head, head group) merges
-  if (tid < (int)nh) {
-    float* pp = p.part + ((size_t)(h0 + tid) * p.S_max + s) * STR;
-    pp[D] = fin_ML[tid][0];
-    pp[D + 1] = fin_ML[tid][1];
-  }
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) is_last = atomicAdd(&p.tickets[bx], 1u) == S_eff - 1 ? 1u : 0u;
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  attn_detail::attn_merge_splits<D, kMThreads>(p, h0, nh, S_eff);
-  if (tid == 0) p.tickets[bx] = 0;  // ready for the next launch
+  if (global_phase && tid == 0) p.tickets[bx] = 0;  // ready for the next launch
 }
 
 template <int D>
 cudaError_t launch_mma_d(cudaStream_t s, const AttnParams& p, bool pdl) {
   constexpr int NST = D == 64 ? 4 : 2;
   constexpr size_t smem = (size_t)kMW * NST * 2 * 16 * (D + 8) * 2;  // per warp: NST stages of a K and a V slice
+  static_assert(smem >= (size_t)kMG * (((64 + 2) * (D + 2) + 4 + 3) / 4 * 4) * 4, "the merge buffer reuses the stages");
   cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   return launch_pdl(attn_mma_kernel<D>, dim3(p.kvH * attn_head_groups(p.qH, p.kvH, kMG), p.S_max), dim3(kMThreads), smem, s,
@@ -305,7 +373,7 @@ bool attn_mma_supported(int kvdtype, uint32_t d) { return kvdtype == 1 && (d == 
 cudaError_t launch_attn_mma(cudaStream_t s, const AttnParams& p, bool pdl) {
   if (p.qH == 0 || p.kvH == 0 || p.qH % p.kvH != 0 || p.S_max == 0 || p.S_max > (uint32_t)attn_detail::kAttnMergeCap || p.out_half) return cudaErrorInvalidValue;
   if (!p.state && p.seq_imm == 0) return cudaErrorInvalidValue;
-  if (((uintptr_t)p.kcache | (uintptr_t)p.vcache) & 15) return cudaErrorInvalidValue;
+  if (((uintptr_t)p.kcache | (uintptr_t)p.vcache | (uintptr_t)p.part) & 15) return cudaErrorInvalidValue;
   switch (p.d) {
     case 64: return launch_mma_d<64>(s, p, pdl);
     case 128: return launch_mma_d<128>(s, p, pdl);

@@ -231,6 +231,31 @@ def test_argmax_ties_pick_the_lowest_index(cuda_ctx, oracle):
     assert int(host(am)[0]) == 0
 
 
+@pytest.mark.parametrize("qH,kvH,d", [(8, 1, 64), (4, 1, 128), (3, 1, 128)])
+@pytest.mark.parametrize("kernel", ["tensor-core", "tile-staged"])
+def test_attention_more_splits_than_one_merge_pass(cuda_ctx, oracle, monkeypatch, qH, kvH, d, kernel):
+    """One KV head (a rank of an 8-way tensor-parallel group) and 70 000 positions: the sequence is cut into more than
+    a hundred splits, so the last CTA merges the partials in several passes with a carried row."""
+    monkeypatch.setenv("NFAI_ATTN_MMA", "1" if kernel == "tensor-core" else "0")
+    monkeypatch.setenv("NFAI_ATTN_RING", "1")
+    seq = 70000
+    rng = np.random.default_rng(seq + d + qH)
+    q = rng.standard_normal(qH * d).astype(np.float32)
+    kc = rng.standard_normal((seq, kvH * d)).astype(np.float16)
+    vc = rng.standard_normal((seq, kvH * d)).astype(np.float16)
+    want = oracle.attention(q, kc.astype(np.float32), vc.astype(np.float32), seq, qH, kvH, d, 1e-5)
+    lib = _lib.load()
+    nbytes = lib.nfai_op_attn_scratch_bytes(qH, kvH, d, seq)
+    scratch = torch.zeros(nbytes // 4 + 1, dtype=torch.float32, device="cuda")
+    dq, dk, dv = dev(q), dev(kc), dev(vc)
+    out = torch.empty(qH * d, dtype=torch.float32, device="cuda")
+    for _ in range(2):
+        out.zero_()
+        call(cuda_ctx, "nfai_op_attn_decode", ptr(dq), ptr(dk), ptr(dv), _lib.F16, seq, qH, kvH, d, ptr(out), ptr(scratch),
+             C.c_size_t(nbytes))
+        assert rel_err(host(out), want) < TOL
+
+
 @pytest.mark.parametrize("qH,kvH,d", [(32, 8, 64), (24, 8, 128), (4, 2, 64), (8, 1, 64), (6, 2, 128)])
 @pytest.mark.parametrize("seq", [1, 2, 15, 16, 17, 100, 255, 256, 257, 700, 5000, 20000, 32768])
 @pytest.mark.parametrize("kernel", ["tensor-core", "tile-staged"])
