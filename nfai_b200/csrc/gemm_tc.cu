@@ -24,6 +24,7 @@
 #include <stdlib.h>
 
 #include <functional>
+#include <type_traits>
 #include <unordered_map>
 
 namespace nfai {
@@ -114,22 +115,49 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 }
 
 // ---- epilogues: two adjacent output columns (n, n+1) of row m; n is even -----------------------------------------
-__device__ __forceinline__ void epilogue_pair(const GemmEpilogue& ep, uint32_t m, uint32_t n, uint32_t N, float a, float b) {
-  switch (ep.kind) {
+// What the epilogue of a pair reads from memory: the residual pair of a plain store, the (cos, sin) of a rotated Q/K
+// pair. The callers fetch it for a whole block of pairs before they touch the accumulators: a loop of load -> add ->
+// store per pair runs at one memory round trip per pair (the store may alias the next load as far as the compiler
+// knows), which cost more than the tile's MMAs.
+// KIND >= 0 fixes the epilogue at compile time (the persistent kernel dispatches once per tile); -1 reads ep.kind.
+template <int KIND = -1>
+__device__ __forceinline__ float2 epilogue_aux(const GemmEpilogue& ep, uint32_t m, uint32_t n, uint32_t N) {
+  switch (KIND >= 0 ? KIND : (int)ep.kind) {
+    case GEMM_EPI_STORE: {
+      if (!ep.resid) break;
+      const float* res = ep.resid + (size_t)m * N;
+      if ((N & 1u) == 0) return __ldcg(reinterpret_cast<const float2*>(res + n));
+      return make_float2(__ldcg(res + n), n + 1 < N ? __ldcg(res + n + 1) : 0.f);
+    }
+    case GEMM_EPI_QKV_ROPE: {
+      if (n < ep.qDim + ep.kvDim) {
+        const uint32_t local = n < ep.qDim ? n : n - ep.qDim;
+        const uint32_t e = local % ep.d;
+        if (e < ep.ropeDim) return ep.rope_cs[(size_t)(ep.pos0 + m) * (ep.ropeDim / 2) + (e >> 1)];
+      }
+      break;
+    }
+    default: break;
+  }
+  return make_float2(0.f, 0.f);
+}
+
+template <int KIND = -1>
+__device__ __forceinline__ void epilogue_pair(const GemmEpilogue& ep, uint32_t m, uint32_t n, uint32_t N, float a, float b,
+                                              const float2 aux) {
+  switch (KIND >= 0 ? KIND : (int)ep.kind) {
     case GEMM_EPI_STORE: {
       float* out = ep.out_f32 + (size_t)m * N;
-      const float* res = ep.resid ? ep.resid + (size_t)m * N : nullptr;
       if ((N & 1u) == 0) {  // rows start on an 8-byte boundary: one store per pair
         float2 r = make_float2(a, b);
-        if (res) {
-          const float2 q = *reinterpret_cast<const float2*>(res + n);
-          r.x += q.x;
-          r.y += q.y;
+        if (ep.resid) {
+          r.x += aux.x;
+          r.y += aux.y;
         }
         *reinterpret_cast<float2*>(out + n) = r;
       } else {
-        out[n] = res ? res[n] + a : a;
-        if (n + 1 < N) out[n + 1] = res ? res[n + 1] + b : b;
+        out[n] = ep.resid ? aux.x + a : a;
+        if (n + 1 < N) out[n + 1] = ep.resid ? aux.y + b : b;
       }
       break;
     }
@@ -146,20 +174,18 @@ __device__ __forceinline__ void epilogue_pair(const GemmEpilogue& ep, uint32_t m
         const uint32_t local = n < ep.qDim ? n : n - ep.qDim;
         const uint32_t e = local % ep.d;
         if (e < ep.ropeDim) {
-          const float2 cs = ep.rope_cs[(size_t)pos * (ep.ropeDim / 2) + (e >> 1)];
+          const float2 cs = aux;
           const float v1 = __fsub_rn(__fmul_rn(cs.x, a), __fmul_rn(cs.y, b));
           const float v2 = __fadd_rn(__fmul_rn(cs.y, a), __fmul_rn(cs.x, b));
           a = v1;
           b = v2;
         }
         if (n < ep.qDim) {
-          float* qrow = ep.out_f32 + (size_t)m * ep.qDim;
-          qrow[n] = a;
-          qrow[n + 1] = b;
+          // (n, local and the row lengths are even: pairs are naturally aligned)
+          *reinterpret_cast<float2*>(ep.out_f32 + (size_t)m * ep.qDim + n) = make_float2(a, b);
         } else if (ep.kv_f16) {
           __half* kc = reinterpret_cast<__half*>(ep.kcache) + (size_t)pos * ep.kvDim + local;
-          kc[0] = __float2half_rn(a);
-          kc[1] = __float2half_rn(b);
+          *reinterpret_cast<__half2*>(kc) = __floats2half2_rn(a, b);
         } else {
           float* kc = reinterpret_cast<float*>(ep.kcache) + (size_t)pos * ep.kvDim + local;
           kc[0] = a;
@@ -169,8 +195,7 @@ __device__ __forceinline__ void epilogue_pair(const GemmEpilogue& ep, uint32_t m
         const uint32_t local = n - ep.qDim - ep.kvDim;
         if (ep.kv_f16) {
           __half* vc = reinterpret_cast<__half*>(ep.vcache) + (size_t)pos * ep.kvDim + local;
-          vc[0] = __float2half_rn(a);
-          vc[1] = __float2half_rn(b);
+          *reinterpret_cast<__half2*>(vc) = __floats2half2_rn(a, b);
         } else {
           float* vc = reinterpret_cast<float*>(ep.vcache) + (size_t)pos * ep.kvDim + local;
           vc[0] = a;
@@ -184,9 +209,12 @@ __device__ __forceinline__ void epilogue_pair(const GemmEpilogue& ep, uint32_t m
 
 // 32 consecutive output columns [n0, n0+32) of row m (n0 is a multiple of 32)
 __device__ __forceinline__ void epilogue_cols(const GemmEpilogue& ep, uint32_t m, uint32_t n0, uint32_t N, const float (&v)[32]) {
+  float2 aux[16];
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) aux[i >> 1] = n0 + i < N ? epilogue_aux(ep, m, n0 + i, N) : make_float2(0.f, 0.f);
 #pragma unroll
   for (int i = 0; i < 32; i += 2)
-    if (n0 + i < N) epilogue_pair(ep, m, n0 + i, N, v[i], v[i + 1]);
+    if (n0 + i < N) epilogue_pair(ep, m, n0 + i, N, v[i], v[i + 1], aux[i >> 1]);
 }
 
 // Split-K: raw partial sums of the same 32 columns into [split][M][N]
@@ -212,7 +240,7 @@ __global__ void __launch_bounds__(256) gemm_finish_kernel(const float* __restric
       a += p[0];
       if (n + 1 < N) b += p[1];
     }
-    epilogue_pair(ep, m, n, N, a, b);
+    epilogue_pair(ep, m, n, N, a, b, epilogue_aux(ep, m, n, N));
   }
 }
 
@@ -440,32 +468,125 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_persistent_kernel(const 
     for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++i) {
       const uint32_t acc = i & 1;
       const uint32_t m0 = (tile % mtiles) * kBM, n0 = (tile / mtiles) * kPBN;
-      ok = bar_wait(tfull0 + 8 * acc, (i >> 1) & 1);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // tcgen05.ld hands every lane one accumulator row; stores along a row would touch 32 different rows per
-      // instruction. The 32 x 32 block goes through shared memory (row stride 33: conflict-free both ways) and comes
-      // back with lanes 0-15 on the column pairs of one row and lanes 16-31 on the next row: 128-byte coalesced rows.
+      // this lane's 16 pairs of a 32 x 32 block: lanes 0-15 along the column pairs of one row, lanes 16-31 on the next
+      const uint32_t col = 2u * (lane & 15);
       float* eb = reinterpret_cast<float*>(gsm + SM::kEpiOff) + (warp - 2) * (32 * 33);
-#pragma unroll 1
-      for (int c = 0; c < kPBN / 32; ++c) {
-        float v[32];
-        tmem_ld32(tmem_base + ((lane_grp * 32u) << 16) + acc * (uint32_t)kPBN + (uint32_t)c * 32u, v);
-        if (m0 + lane_grp * 32 < M && n0 + c * 32 < N) {  // warp-uniform
+      // One instance per epilogue kind, chosen once per tile: the loops below are straight-line code for that kind.
+      auto tile_epilogue = [&](auto kind_c) -> bool {
+        constexpr int KIND = decltype(kind_c)::value;
+        constexpr bool kAux = KIND != GEMM_EPI_SILU_MUL;  // residual pairs / (cos, sin) pairs come from memory
+        float2 aux[16];
+        // Q/K/V columns: everything that depends on the column only (which of Q, K, V; the position inside the head;
+        // whether the pair is rotated) is the same for the 16 pairs of a lane in one block and is worked out once.
+        struct ColInfo {
+          uint32_t seg, local, half_e;  // 0 = Q, 1 = K, 2 = V; column inside the segment; index into a (cos, sin) row
+          bool rot, live;
+        };
+        auto col_info = [&](int c) {
+          ColInfo ci;
+          const uint32_t n = n0 + c * 32 + col;
+          ci.live = n < N;
+          ci.seg = n < ep.qDim ? 0u : n < ep.qDim + ep.kvDim ? 1u : 2u;
+          ci.local = n - (ci.seg == 0 ? 0u : ci.seg == 1 ? ep.qDim : ep.qDim + ep.kvDim);
+          const uint32_t e = ci.local & (ep.d - 1);  // head dimensions are powers of two (32, 64, 128)
+          ci.rot = ci.seg < 2 && e < ep.ropeDim;
+          ci.half_e = e >> 1;
+          return ci;
+        };
+        auto load_aux = [&](int c) {
+          if constexpr (KIND == GEMM_EPI_QKV_ROPE) {
+            const ColInfo ci = col_info(c);
+            const float2* cs = ep.rope_cs + (size_t)(ep.pos0 + m0 + lane_grp * 32 + (lane >> 4)) * (ep.ropeDim / 2) + ci.half_e;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) eb[lane * 33 + i] = v[i];
-          __syncwarp();
-          const uint32_t col = 2u * (lane & 15);
-#pragma unroll 4
-          for (int rr = 0; rr < 16; ++rr) {
-            const uint32_t row = 2u * rr + (lane >> 4);
-            const uint32_t m = m0 + lane_grp * 32 + row, n = n0 + c * 32 + col;
-            if (m < M && n < N) epilogue_pair(ep, m, n, N, eb[row * 33 + col], eb[row * 33 + col + 1]);
+            for (int rr = 0; rr < 16; ++rr) {
+              const uint32_t m = m0 + lane_grp * 32 + 2u * rr + (lane >> 4);
+              aux[rr] = ci.rot && ci.live && m < M ? cs[(size_t)(2 * rr) * (ep.ropeDim / 2)] : make_float2(1.f, 0.f);
+            }
+          } else if constexpr (kAux) {
+#pragma unroll
+            for (int rr = 0; rr < 16; ++rr) {
+              const uint32_t m = m0 + lane_grp * 32 + 2u * rr + (lane >> 4), n = n0 + c * 32 + col;
+              aux[rr] = m < M && n < N ? epilogue_aux<KIND>(ep, m, n, N) : make_float2(0.f, 0.f);
+            }
           }
-          __syncwarp();
+        };
+        load_aux(0);  // on its way while the tensor pipe still works on this tile
+        bool good = bar_wait(tfull0 + 8 * acc, (i >> 1) & 1);
+        good = __all_sync(0xffffffffu, good);
+        if (!good) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // tcgen05.ld hands every lane one accumulator row; stores along a row would touch 32 different rows per
+        // instruction. The 32 x 32 block goes through shared memory (row stride 33: conflict-free both ways) and comes
+        // back with lanes 0-15 on the column pairs of one row and lanes 16-31 on the next row: 128-byte coalesced rows.
+#pragma unroll 1
+        for (int c = 0; c < kPBN / 32; ++c) {
+          float v[32];
+          tmem_ld32(tmem_base + ((lane_grp * 32u) << 16) + acc * (uint32_t)kPBN + (uint32_t)c * 32u, v);
+          const bool live = m0 + lane_grp * 32 < M && n0 + c * 32 < N;  // warp-uniform
+          if (live) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) eb[lane * 33 + e] = v[e];
+            __syncwarp();
+          }
+          float2 cur[16];
+          if constexpr (kAux) {
+#pragma unroll
+            for (int rr = 0; rr < 16; ++rr) cur[rr] = aux[rr];
+            if (c + 1 < kPBN / 32) load_aux(c + 1);  // the next block's reads are in flight during this block's stores
+          }
+          if constexpr (KIND == GEMM_EPI_QKV_ROPE) {
+            if (live) {
+              const ColInfo ci = col_info(c);
+              const uint32_t mrow = m0 + lane_grp * 32 + (lane >> 4);  // rows mrow, mrow + 2, ...
+              if (ci.live) {
+                // destination of row mrow; the next pair of this lane lies two rows (positions) further on
+                float* qd = ep.out_f32 + (size_t)mrow * ep.qDim + ci.local;
+                const size_t kvoff = (size_t)(ep.pos0 + mrow) * ep.kvDim + ci.local;
+                void* const cache = ci.seg == 1 ? ep.kcache : ep.vcache;
+#pragma unroll
+                for (int rr = 0; rr < 16; ++rr) {
+                  const uint32_t row = 2u * rr + (lane >> 4);
+                  if (mrow + 2u * rr >= M) break;
+                  float a = eb[row * 33 + col], b = eb[row * 33 + col + 1];
+                  if (ci.rot) {  // value1 = cos*a - sin*b ; value2 = sin*a + cos*b, products rounded separately
+                    const float2 cs = cur[rr];
+                    const float v1 = __fsub_rn(__fmul_rn(cs.x, a), __fmul_rn(cs.y, b));
+                    const float v2 = __fadd_rn(__fmul_rn(cs.y, a), __fmul_rn(cs.x, b));
+                    a = v1;
+                    b = v2;
+                  }
+                  if (ci.seg == 0) {
+                    *reinterpret_cast<float2*>(qd + (size_t)(2 * rr) * ep.qDim) = make_float2(a, b);
+                  } else if (ep.kv_f16) {
+                    *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(cache) + kvoff + (size_t)(2 * rr) * ep.kvDim) =
+                        __floats2half2_rn(a, b);
+                  } else {
+                    *reinterpret_cast<float2*>(reinterpret_cast<float*>(cache) + kvoff + (size_t)(2 * rr) * ep.kvDim) =
+                        make_float2(a, b);
+                  }
+                }
+              }
+              __syncwarp();
+            }
+          } else if (live) {
+#pragma unroll(kAux ? 16 : 4)
+            for (int rr = 0; rr < 16; ++rr) {
+              const uint32_t row = 2u * rr + (lane >> 4);
+              const uint32_t m = m0 + lane_grp * 32 + row, n = n0 + c * 32 + col;
+              if (m < M && n < N)
+                epilogue_pair<KIND>(ep, m, n, N, eb[row * 33 + col], eb[row * 33 + col + 1], kAux ? cur[rr] : make_float2(0.f, 0.f));
+            }
+            __syncwarp();
+          }
         }
+        return true;
+      };
+      switch (ep.kind) {
+        case GEMM_EPI_STORE: ok = tile_epilogue(std::integral_constant<int, (int)GEMM_EPI_STORE>{}); break;
+        case GEMM_EPI_SILU_MUL: ok = tile_epilogue(std::integral_constant<int, (int)GEMM_EPI_SILU_MUL>{}); break;
+        default: ok = tile_epilogue(std::integral_constant<int, (int)GEMM_EPI_QKV_ROPE>{}); break;
       }
+      if (!ok) break;
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) bar_arrive(tempty0 + 8 * acc);
