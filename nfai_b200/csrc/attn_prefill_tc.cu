@@ -84,12 +84,15 @@ __global__ void __launch_bounds__(kPThreads, D == 64 ? 2 : 1) attn_prefill_tc_ke
   pdl_wait();  // q and the chunk's cache rows come from the QKV GEMM launched just before
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qr = lane >> 2, qc = (lane & 3) * 2;
-  const uint32_t h = blockIdx.y;
+  // Causal work grows with the token tile: CTAs are numbered so that the last (longest) tiles of all heads start
+  // first and the short ones fill the gaps at the end.
+  const uint32_t h = blockIdx.x % p.qH;
+  const uint32_t tile_x = gridDim.x / p.qH - 1 - blockIdx.x / p.qH;
   const uint32_t g = h / (p.qH / p.kvH);
   const uint32_t kvDim = p.kvH * D, qDim = p.qH * D;
   const uint32_t p0 = p.seq_imm - 1;  // position of the chunk's first token
-  const uint32_t row_a = blockIdx.x * kPM + warp * 16 + qr, row_b = row_a + 8;  // this thread's two token rows
-  const uint32_t rows_end = min(T, (blockIdx.x + 1) * (uint32_t)kPM);           // tokens of this CTA end here
+  const uint32_t row_a = tile_x * kPM + warp * 16 + qr, row_b = row_a + 8;  // this thread's two token rows
+  const uint32_t rows_end = min(T, (tile_x + 1) * (uint32_t)kPM);           // tokens of this CTA end here
   const uint32_t kv_end = p0 + rows_end;                                         // positions [0, kv_end) are needed
 
   // Q fragments (A operand, 16 x 16 per k step), scaled into the base-2 domain
@@ -164,7 +167,7 @@ __global__ void __launch_bounds__(kPThreads, D == 64 ? 2 : 1) attn_prefill_tc_ke
     const uint32_t ks_s = ks_base + (it & 1) * (uint32_t)(kTile * 2), vs_s = vs_base + (it & 1) * (uint32_t)(kTile * 2);
     // a warp whose rows all lie before this tile's first position has nothing to add (causal), but it keeps
     // taking part in the block barriers
-    const uint32_t warp_last_pos = p0 + blockIdx.x * kPM + warp * 16 + 15;
+    const uint32_t warp_last_pos = p0 + tile_x * kPM + warp * 16 + 15;
     if (n0 <= warp_last_pos) {
     // ---- S = Q K^T : 16 rows x 64 positions per warp
     float s[kPN / 8][4];
@@ -181,7 +184,7 @@ __global__ void __launch_bounds__(kPThreads, D == 64 ? 2 : 1) attn_prefill_tc_ke
       }
     }
     // ---- causal mask (only tiles that reach past the warp's first row need it)
-    if (n0 + kPN - 1 > p0 + blockIdx.x * kPM + warp * 16) {
+    if (n0 + kPN - 1 > p0 + tile_x * kPM + warp * 16) {
       const uint32_t lim_a = row_a < T ? p0 + row_a : 0u, lim_b = row_b < T ? p0 + row_b : 0u;  // last visible position
       const bool va = row_a < T, vb = row_b < T;
 #pragma unroll
@@ -274,7 +277,7 @@ cudaError_t launch_ptc_d(cudaStream_t s, const AttnParams& p, uint32_t T) {
     if (e != cudaSuccess) return e;
     attr_device = dev;
   }
-  dim3 grid((T + kPM - 1) / kPM, p.qH);
+  dim3 grid(((T + kPM - 1) / kPM) * p.qH);
   return launch_pdl(attn_prefill_tc_kernel<KVT, D>, grid, dim3(kPThreads), smem, s, prefill_pdl(), p, T);
 }
 

@@ -370,8 +370,8 @@ struct PSmem {
   static constexpr uint32_t kBBytes = kPBN * kBK * 2;
   static constexpr uint32_t kStage = kABytes + kBBytes;
   static constexpr uint32_t kBarOff = kPStages * kStage;
-  static constexpr uint32_t kEpiOff = kBarOff + 256;             // 4 warps x 32 x 33 floats: accumulator block turned
-  static constexpr uint32_t kEpiBytes = 4 * 32 * 33 * 4;         // so that lanes run along a row of the output
+  static constexpr uint32_t kEpiOff = kBarOff + 256;             // 8 warps x 32 x 33 floats: accumulator block turned
+  static constexpr uint32_t kEpiBytes = 8 * 32 * 33 * 4;         // so that lanes run along a row of the output
   static constexpr uint32_t kTotal = kEpiOff + kEpiBytes + 1024;
 };
 
@@ -379,7 +379,12 @@ __device__ __forceinline__ void bar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-__global__ void __launch_bounds__(kGemmThreads) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap mapA,
+// Eight epilogue warps, two per quarter of the tensor-memory lanes (a warp may only read the lanes of its index modulo 4),
+// each pair sharing the column blocks of its rows: with one warp per scheduler the SiLU epilogue (an exponential and
+// an IEEE division per output) ran at the latency of its dependent instructions and took longer than the tile's MMAs.
+constexpr int kPThreadsGemm = 64 + 8 * 32;
+static_assert(PSmem::kTotal <= 227 * 1024, "shared memory of the persistent kernel");
+__global__ void __launch_bounds__(kPThreadsGemm) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap mapA,
                                                                           const __grid_constant__ CUtensorMap mapW, uint32_t M,
                                                                           uint32_t N, uint32_t K, const GemmEpilogue ep,
                                                                           uint32_t* err) {
@@ -403,7 +408,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_persistent_kernel(const 
     }
     for (int a = 0; a < 2; ++a) {
       bar_init(tfull0 + 8 * a, 1);
-      bar_init(tempty0 + 8 * a, 4);  // one arrival per epilogue warp
+      bar_init(tempty0 + 8 * a, 8);  // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -510,7 +515,8 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_persistent_kernel(const 
             }
           }
         };
-        load_aux(0);  // on its way while the tensor pipe still works on this tile
+        const int c_first = (warp - 2) >> 2;  // this warp's column blocks: c_first, c_first + 2, ...
+        load_aux(c_first);  // on its way while the tensor pipe still works on this tile
         bool good = bar_wait(tfull0 + 8 * acc, (i >> 1) & 1);
         good = __all_sync(0xffffffffu, good);
         if (!good) return false;
@@ -519,7 +525,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_persistent_kernel(const 
         // instruction. The 32 x 32 block goes through shared memory (row stride 33: conflict-free both ways) and comes
         // back with lanes 0-15 on the column pairs of one row and lanes 16-31 on the next row: 128-byte coalesced rows.
 #pragma unroll 1
-        for (int c = 0; c < kPBN / 32; ++c) {
+        for (int c = c_first; c < kPBN / 32; c += 2) {
           float v[32];
           tmem_ld32(tmem_base + ((lane_grp * 32u) << 16) + acc * (uint32_t)kPBN + (uint32_t)c * 32u, v);
           const bool live = m0 + lane_grp * 32 < M && n0 + c * 32 < N;  // warp-uniform
@@ -532,7 +538,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_persistent_kernel(const 
           if constexpr (kAux) {
 #pragma unroll
             for (int rr = 0; rr < 16; ++rr) cur[rr] = aux[rr];
-            if (c + 1 < kPBN / 32) load_aux(c + 1);  // the next block's reads are in flight during this block's stores
+            if (c + 2 < kPBN / 32) load_aux(c + 2);  // the next block's reads are in flight during this block's stores
           }
           if constexpr (KIND == GEMM_EPI_QKV_ROPE) {
             if (live) {
@@ -569,7 +575,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_tc_persistent_kernel(const 
               __syncwarp();
             }
           } else if (live) {
-#pragma unroll(kAux ? 16 : 4)
+#pragma unroll
             for (int rr = 0; rr < 16; ++rr) {
               const uint32_t row = 2u * rr + (lane >> 4);
               const uint32_t m = m0 + lane_grp * 32 + row, n = n0 + c * 32 + col;
@@ -730,7 +736,7 @@ cudaError_t launch_persistent(cudaStream_t s, const __half* A, const __half* W, 
     attr_device = dev;
   }
   const uint32_t tiles = ((M + kBM - 1) / kBM) * ((N + kPBN - 1) / kPBN);
-  return launch_pdl(gemm_tc_persistent_kernel, dim3(tiles < sm_count() ? tiles : sm_count()), dim3(kGemmThreads), PSmem::kTotal, s,
+  return launch_pdl(gemm_tc_persistent_kernel, dim3(tiles < sm_count() ? tiles : sm_count()), dim3(kPThreadsGemm), PSmem::kTotal, s,
                     prefill_pdl(), mapA, mapW, M, N, K, ep, err);
 }
 
