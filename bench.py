@@ -220,7 +220,7 @@ def run_ours(args, cfg):
         torch.cuda.synchronize()
 
     K, W = args.steps, max(args.warmup, 3)
-    ctx_size = PROMPT_LEN + W + K + 8
+    ctx_size = PROMPT_LEN + max(W + K, 16) + 8  # room for the parity check's 15 greedy steps whatever K is
     factory = LlamaModelFactory(local_rank, rank, world, uid)
     exchange = "none"
     if world > 1:
