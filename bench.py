@@ -35,7 +35,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel (FFN gate/up GEMV of configs[1]
 # on one GPU), from an ncu capture of this kernel; it goes stale when the kernel's memory behaviour changes, so the
 # capture it came from is named beside it.
-NCU_TRAFFIC = {("c1", 1): {"bytes": 67165440 + 270848,
+NCU_TRAFFIC = {("c1", 1): {"bytes": 67165440 + 710400,
                            "capture": "ncu --set full --clock-control none -k regex:gemv_kernel -s 170 -c 4 of "
                                       "bench.py --steps 2 --warmup 3 --prompt-len 2 --min-timed-s 0: the gate/up launch "
                                       "(67.165 MB read + 0.271 MB written against 67.117 MB algorithmic)"}}
