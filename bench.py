@@ -38,7 +38,7 @@ FALLBACK_HBM_GBS = 6650.0
 NCU_TRAFFIC = {("c1", 1): {"bytes": 67165440 + 710400,
                            "capture": "ncu --set full --clock-control none -k regex:gemv_kernel -s 170 -c 4 of "
                                       "bench.py --steps 2 --warmup 3 --prompt-len 2 --min-timed-s 0: the gate/up launch "
-                                      "(67.165 MB read + 0.271 MB written against 67.117 MB algorithmic)"}}
+                                      "(67.165 MB read + 0.710 MB written against 67.117 MB algorithmic)"}}
 PROMPT_LEN = 128
 MIN_TIMED_S = 1.0  # the K-step loop is repeated until this much device time has been measured; the median is reported
 
