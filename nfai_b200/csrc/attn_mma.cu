@@ -80,7 +80,6 @@ __global__ void __launch_bounds__(kMThreads, 1) attn_mma_kernel(const AttnParams
   constexpr int LD = D + 8;               // shared-memory row stride in halves (16 bytes of padding: conflict-free ldmatrix)
   constexpr int kSlice = PW * LD;         // halves of one K (or V) slice
   constexpr int STR = D + 2;              // one partial in scratch: D accumulators, m, l
-  constexpr int SSTR = D + 4;
   extern __shared__ __align__(16) unsigned char mma_smem[];
   constexpr int kRowsMax = 64;                                // rows of partials merged per pass
   constexpr int kRegion = ((kRowsMax + 2) * STR + 4 + 3) / 4 * 4;  // floats per head in the merge buffer
