@@ -7,9 +7,10 @@
 //                pre-multiplied by 1/sqrt(d) * log2(e) so every exponential is one ex2)
 //   online softmax on the accumulator fragments (running max and sum per token row, quad shuffles)
 //   O += P V    (the S accumulators are re-packed as the A operand; V is read transposed with ldmatrix.trans)
-// K and V tiles are staged in shared memory (rows padded by 16 bytes: conflict-free ldmatrix) in two buffers: tile
-// i + 1 is copied with cp.async (16 bytes per copy, zero-filled past the range) while tile i is multiplied; a float32
-// cache is converted to float16 on the way in with plain loads instead.
+// K and V tiles are staged in shared memory (rows padded by 16 bytes: conflict-free ldmatrix) in three buffers: tiles
+// i + 1 and i + 2 are being copied with cp.async (16 bytes per copy, zero-filled past the range) while tile i is
+// multiplied, and one block barrier per tile suffices; a float32 cache is converted to float16 on the way in with
+// plain loads instead.
 // Token t of the chunk sits at position p0 + t and attends to positions 0 .. p0 + t (causal); rows past the
 // chunk and positions past the last token are masked with -inf, and V rows past the range are zero-filled so that
 // a zero weight never meets a non-finite stale value.
@@ -29,6 +30,7 @@ namespace {
 constexpr int kPM = 128;      // tokens per CTA
 constexpr int kPN = 64;       // positions per K/V tile
 constexpr int kPThreads = 256;
+constexpr int kBufs = 3;      // K/V tile buffers
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -78,8 +80,8 @@ __global__ void __launch_bounds__(kPThreads, D == 64 ? 2 : 1) attn_prefill_tc_ke
   constexpr int LD = D + 8;  // shared-memory row stride in halves (16 bytes of padding)
   constexpr int kTile = kPN * LD;  // halves of one K (or V) tile
   extern __shared__ __align__(16) unsigned char ptc_smem[];
-  __half* const Ks = reinterpret_cast<__half*>(ptc_smem);  // [2][kTile]
-  __half* const Vs = Ks + 2 * kTile;                        // [2][kTile]
+  __half* const Ks = reinterpret_cast<__half*>(ptc_smem);  // [kBufs][kTile]
+  __half* const Vs = Ks + kBufs * kTile;                    // [kBufs][kTile]
   pdl_launch_dependents();
   pdl_wait();  // q and the chunk's cache rows come from the QKV GEMM launched just before
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -156,15 +158,20 @@ __global__ void __launch_bounds__(kPThreads, D == 64 ? 2 : 1) attn_prefill_tc_ke
     }
   };
   const uint32_t ntiles = (kv_end + kPN - 1) / kPN;
+  // Three buffers: tile it + 2 is requested into the buffer that tile it - 1 was multiplied from, right after the one
+  // block barrier of the iteration (which says both that tile it has landed everywhere and that every warp is done
+  // with tile it - 1); two tiles are in flight while one is multiplied.
   issue(0, 0);
   cp_async_commit();
+  if (ntiles > 1) issue(1, 1);
+  cp_async_commit();  // (an empty group keeps the count uniform)
   for (uint32_t it = 0; it < ntiles; ++it) {
     const uint32_t n0 = it * kPN;
-    if (it + 1 < ntiles) issue((int)((it + 1) & 1), it + 1);  // into the buffer every warp left at the end of iteration it - 1
-    cp_async_commit();                                         // (an empty group keeps the count uniform)
-    cp_async_wait_all_but_one();                               // this thread's copies of tile it have landed
-    __syncthreads();                                           // ... and everybody else's
-    const uint32_t ks_s = ks_base + (it & 1) * (uint32_t)(kTile * 2), vs_s = vs_base + (it & 1) * (uint32_t)(kTile * 2);
+    cp_async_wait_all_but_one();  // this thread's copies of tile it have landed
+    __syncthreads();              // ... and everybody else's; every warp has left tile it - 1
+    if (it + 2 < ntiles) issue((int)((it + 2) % kBufs), it + 2);
+    cp_async_commit();
+    const uint32_t ks_s = ks_base + (it % kBufs) * (uint32_t)(kTile * 2), vs_s = vs_base + (it % kBufs) * (uint32_t)(kTile * 2);
     // a warp whose rows all lie before this tile's first position has nothing to add (causal), but it keeps
     // taking part in the block barriers
     const uint32_t warp_last_pos = p0 + tile_x * kPM + warp * 16 + 15;
@@ -244,7 +251,6 @@ __global__ void __launch_bounds__(kPThreads, D == 64 ? 2 : 1) attn_prefill_tc_ke
       }
     }
     }  // tile visible to this warp
-    __syncthreads();  // every warp has left this buffer: the next iteration refills it
   }
   // ---- normalise and store (float16: the A operand of the output projection)
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
@@ -267,7 +273,7 @@ __global__ void __launch_bounds__(kPThreads, D == 64 ? 2 : 1) attn_prefill_tc_ke
 
 template <typename KVT, int D>
 cudaError_t launch_ptc_d(cudaStream_t s, const AttnParams& p, uint32_t T) {
-  constexpr size_t smem = (size_t)4 * kPN * (D + 8) * 2;  // two buffers of a K and a V tile
+  constexpr size_t smem = (size_t)2 * kBufs * kPN * (D + 8) * 2;  // kBufs buffers of a K and a V tile
   static thread_local int attr_device = -1;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
