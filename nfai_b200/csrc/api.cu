@@ -1092,6 +1092,7 @@ static int prefill_batched(nfai_model* m, const uint32_t* tokens, int n) {
   const size_t kvs = dtype_size(kvdt);
   uint32_t* err = &m->state->err;
   uint32_t pos0 = m->pos;
+  const bool tp_on = c->world > 1;
   int done = 0;
   while (done < n) {
     const uint32_t T = (uint32_t)(n - done) < m->pf_chunk ? (uint32_t)(n - done) : m->pf_chunk;
@@ -1102,7 +1103,7 @@ static int prefill_batched(nfai_model* m, const uint32_t* tokens, int n) {
       const LayerW& L = m->layers[l];
       char* kcl = (char*)m->kc + (size_t)l * kv_layer_elems(m) * kvs;
       char* vcl = (char*)m->vc + (size_t)l * kv_layer_elems(m) * kvs;
-      CU(c, launch_rmsnorm_to_half(s, m->pfX0, L.attn_norm.ptr, hp.eps, T, hp.H, m->pfA));
+      CU(c, launch_rmsnorm_to_half(s, m->pfX0, L.attn_norm.ptr, hp.eps, T, hp.H, m->pfA, tp_on && l > 0));
       GemmEpilogue eq;
       eq.kind = GEMM_EPI_QKV_ROPE;
       eq.scratch = m->pfPart; eq.scratch_floats = m->pfPartFloats;
@@ -1116,14 +1117,13 @@ static int prefill_batched(nfai_model* m, const uint32_t* tokens, int n) {
       else CU(c, launch_attn_prefill(s, kvdt, a, T));
       // Tensor parallel: the O and down GEMMs produce this rank's partial [T][H]; rank 0 adds the residual into its
       // partial and one NCCL all-reduce per GEMM makes the sums (bit-identical on every rank).
-      const bool tp_on = c->world > 1;
       const bool add_resid = !tp_on || c->rank == 0;
       GemmEpilogue eo;
       eo.kind = GEMM_EPI_STORE; eo.out_f32 = m->pfX1; eo.resid = add_resid ? m->pfX0 : nullptr;
       eo.scratch = m->pfPart; eo.scratch_floats = m->pfPartFloats;
       CU(c, launch_gemm_tc(s, m->pfAO, (const __half*)L.o.ptr, T, hp.H, m->qDimL, eo, err));
       if (tp_on) CU(c, tp_allreduce(c->tp, s, m->pfX1, (size_t)T * hp.H));
-      CU(c, launch_rmsnorm_to_half(s, m->pfX1, L.ffn_norm.ptr, hp.eps, T, hp.H, m->pfA));
+      CU(c, launch_rmsnorm_to_half(s, m->pfX1, L.ffn_norm.ptr, hp.eps, T, hp.H, m->pfA, tp_on));
       GemmEpilogue eg;
       eg.kind = GEMM_EPI_SILU_MUL; eg.out_f16 = m->pfH;
       eg.scratch = m->pfPart; eg.scratch_floats = m->pfPartFloats;

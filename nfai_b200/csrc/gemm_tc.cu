@@ -779,8 +779,8 @@ bool prefill_pdl() {
 }
 
 cudaError_t launch_rmsnorm_to_half(cudaStream_t s, const float* x, const float* gain, float eps, uint32_t M, uint32_t H,
-                                   __half* out) {
-  return launch_pdl(rmsnorm_to_half_kernel, dim3(M), dim3(256), 0, s, prefill_pdl(), x, gain, eps, H, out);
+                                   __half* out, bool after_collective) {
+  return launch_pdl(rmsnorm_to_half_kernel, dim3(M), dim3(256), 0, s, prefill_pdl() && !after_collective, x, gain, eps, H, out);
 }
 
 cudaError_t launch_embed_rows(cudaStream_t s, const __half* E, const uint32_t* tokens, uint32_t M, uint32_t H, float* x) {

@@ -35,8 +35,10 @@ cudaError_t launch_gemm_tc(cudaStream_t s, const __half* A, const __half* W, uin
                            const GemmEpilogue& ep, uint32_t* err);
 
 // x[M][H] float32 -> RMS-normalised, gain-scaled float16 rows (the A operand of the QKV and gate/up GEMMs).
+// after_collective: x was produced by a library collective enqueued just before; the kernel is then launched with
+// plain stream order (no programmatic dependent launch across the library's kernels).
 cudaError_t launch_rmsnorm_to_half(cudaStream_t s, const float* x, const float* gain, float eps, uint32_t M, uint32_t H,
-                                   __half* out);
+                                   __half* out, bool after_collective = false);
 // rows of the embedding matrix (float16) widened to float32: x[t] = E[tokens[t]].
 cudaError_t launch_embed_rows(cudaStream_t s, const __half* E, const uint32_t* tokens, uint32_t M, uint32_t H, float* x);
 cudaError_t launch_float_to_half(cudaStream_t s, const float* in, __half* out, size_t n);
